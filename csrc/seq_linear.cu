@@ -1,0 +1,169 @@
+// Linear layers for any shape and for bfloat16 or true float32 operands: y = act(x W^T) with W [N, K] (out, in).
+//
+//  * linear_rows_kernel  (M <= 8: decode)  — weight-streaming: a warp owns ROWS output features, reads their weight rows once
+//    (16-byte loads where the pitch allows) and keeps ROWS x M fp32 accumulators; activations come from L1.
+//  * linear_tiled_kernel (any M)           — 64 x 64 x 16 shared-memory tiles, 4 x 4 outputs per thread, fp32 FMA.  This is
+//    the exact float32 path and the fall-back for pitches the tensor-core GEMM does not take.
+//
+// Products and sums are fp32 (fmaf), never TF32.  The output is fp32 or the operand type, written at a column offset
+// of a wider row (ldo) so that projections that share an input can share an output buffer.
+#include "jllama_b200.h"
+#include "seq_types.cuh"
+
+namespace jl {
+
+constexpr int LR_ROWS = 4;      // output features per warp
+constexpr int LR_MAXM = 8;
+
+template <typename T> struct Vec;                    // 16-byte vector of T
+template <> struct Vec<float> { static constexpr int N = 4; };
+template <> struct Vec<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename T> __device__ __forceinline__ void load_vec(const T* p, float (&v)[Vec<T>::N]);
+template <> __device__ __forceinline__ void load_vec<float>(const float* p, float (&v)[4]) {
+  float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  uint4 t = *reinterpret_cast<const uint4*>(p);
+  v[0] = bf16_lo(t.x); v[1] = bf16_hi(t.x); v[2] = bf16_lo(t.y); v[3] = bf16_hi(t.y);
+  v[4] = bf16_lo(t.z); v[5] = bf16_hi(t.z); v[6] = bf16_lo(t.w); v[7] = bf16_hi(t.w);
+}
+
+template <typename T, typename OutT, int M>
+__global__ void __launch_bounds__(128) linear_rows_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w,
+                                                          OutT* __restrict__ out, int ldo, int N, int K, int act, float p0,
+                                                          float p1, int vec_ok) {
+  const int lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * LR_ROWS;
+  if (n0 >= N) return;
+  float acc[LR_ROWS][M];
+#pragma unroll
+  for (int r = 0; r < LR_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+  constexpr int VN = Vec<T>::N;
+  int k_done = 0;
+  if (vec_ok) {
+    const int kv = K / VN * VN;
+    for (int k = lane * VN; k < kv; k += 32 * VN) {
+      float xv[M][VN];
+#pragma unroll
+      for (int m = 0; m < M; ++m) load_vec<T>(x + (size_t)m * ldx + k, xv[m]);
+#pragma unroll
+      for (int r = 0; r < LR_ROWS; ++r) {
+        if (n0 + r < N) {
+          float wv[VN];
+          load_vec<T>(w + (size_t)(n0 + r) * K + k, wv);
+#pragma unroll
+          for (int m = 0; m < M; ++m)
+#pragma unroll
+            for (int j = 0; j < VN; ++j) acc[r][m] = fmaf(wv[j], xv[m][j], acc[r][m]);
+        }
+      }
+    }
+    k_done = kv;
+  }
+  for (int k = k_done + lane; k < K; k += 32) {
+#pragma unroll
+    for (int r = 0; r < LR_ROWS; ++r) {
+      if (n0 + r < N) {
+        const float wv = to_f(w[(size_t)(n0 + r) * K + k]);
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = fmaf(wv, to_f(x[(size_t)m * ldx + k]), acc[r][m]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < LR_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const float s = warp_sum(acc[r][m]);
+      if (lane == 0 && n0 + r < N) out[(size_t)m * ldo + n0 + r] = from_f<OutT>(apply_act(s, act, p0, p1));
+    }
+}
+
+constexpr int LT_BM = 64, LT_BN = 64, LT_BK = 16;
+
+template <typename T, typename OutT>
+__global__ void __launch_bounds__(256) linear_tiled_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w,
+                                                           OutT* __restrict__ out, int ldo, int M, int N, int K, int act,
+                                                           float p0, float p1) {
+  __shared__ float xs[LT_BK][LT_BM + 4];
+  __shared__ float ws[LT_BK][LT_BN + 4];
+  const int m0 = blockIdx.y * LT_BM, n0 = blockIdx.x * LT_BN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;         // 16 x 16 threads, 4 x 4 outputs each
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += LT_BK) {
+    for (int i = threadIdx.x; i < LT_BM * LT_BK; i += 256) {
+      const int r = i / LT_BK, c = i % LT_BK;
+      const int gm = m0 + r, gn = n0 + r, gk = k0 + c;
+      xs[c][r] = (gm < M && gk < K) ? to_f(x[(size_t)gm * ldx + gk]) : 0.0f;
+      ws[c][r] = (gn < N && gk < K) ? to_f(w[(size_t)gn * K + gk]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < LT_BK; ++c) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = xs[c][ty * 4 + i]; b[i] = ws[c][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < N) out[(size_t)gm * ldo + gn] = from_f<OutT>(apply_act(acc[i][j], act, p0, p1));
+    }
+  }
+}
+
+template <typename T, typename OutT>
+static int launch_linear(const void* x, int ldx, const void* w, void* out, int ldo, int M, int N, int K, int act, float p0,
+                         float p1, cudaStream_t st) {
+  count_launch();
+  if (M <= LR_MAXM) {
+    constexpr int VN = Vec<T>::N;
+    const int vec_ok = (K % VN == 0) && (ldx % VN == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0);
+    const int warps = 4, blocks = ((N + LR_ROWS - 1) / LR_ROWS + warps - 1) / warps;
+#define JL_LR(MM)                                                                                                       \
+  case MM:                                                                                                              \
+    linear_rows_kernel<T, OutT, MM><<<blocks, warps * 32, 0, st>>>((const T*)x, ldx, (const T*)w, (OutT*)out, ldo, N, K, act, \
+                                                                   p0, p1, vec_ok);                                     \
+    break;
+    switch (M) { JL_LR(1) JL_LR(2) JL_LR(3) JL_LR(4) JL_LR(5) JL_LR(6) JL_LR(7) JL_LR(8) }
+#undef JL_LR
+  } else {
+    dim3 grid((N + LT_BN - 1) / LT_BN, (M + LT_BM - 1) / LT_BM);
+    linear_tiled_kernel<T, OutT><<<grid, 256, 0, st>>>((const T*)x, ldx, (const T*)w, (OutT*)out, ldo, M, N, K, act, p0, p1);
+  }
+  return cudaGetLastError() == cudaSuccess ? JL_OK : JL_ERR_CUDA;
+}
+
+}  // namespace jl
+
+using namespace jl;
+
+extern "C" JL_API int jl_linear_any(const void* x, int ldx, const void* w, void* out, int ldo, int M, int N, int K, int act,
+                                    float p0, float p1, int dtype, int out_f32, void* stream) {
+  JL_CHECK_ARG(M >= 1 && N >= 1 && K >= 1 && ldx >= K && ldo >= N, "jl_linear_any: bad shape M=%d N=%d K=%d ldx=%d ldo=%d", M, N,
+               K, ldx, ldo);
+  JL_CHECK_ARG(act >= 0 && act <= ACT_SCALE_SOFTCAP, "jl_linear_any: bad activation %d", act);
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc;
+  if (dtype == DT_BF16)
+    rc = out_f32 ? launch_linear<__nv_bfloat16, float>(x, ldx, w, out, ldo, M, N, K, act, p0, p1, st)
+                 : launch_linear<__nv_bfloat16, __nv_bfloat16>(x, ldx, w, out, ldo, M, N, K, act, p0, p1, st);
+  else
+    rc = launch_linear<float, float>(x, ldx, w, out, ldo, M, N, K, act, p0, p1, st);
+  if (rc != JL_OK) return cuda_fail(cudaGetLastError(), "jl_linear_any launch");
+  return JL_OK;
+}

@@ -1,0 +1,134 @@
+// Row-wise kernels of the models whose residual stream is float32: embedding into fp32, RMS norm with a weight offset
+// (weight stored around zero: offset 1; plain weight: offset 0), the "norm after the sublayer + residual add + norm
+// before the next sublayer" fusion, per-head norm with an output gate, and the activation / cast pass that follows a
+// tensor-core GEMM.  All statistics in fp32, exact math (no fast-math for this file).
+#include "jllama_b200.h"
+#include "seq_types.cuh"
+
+namespace jl {
+
+template <typename T>
+__global__ void embed_f32_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int W,
+                                 int V) {
+  const int m = blockIdx.x;
+  int id = ids[m];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  const T* row = table + (size_t)id * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)m * W + i] = to_f(row[i]);
+}
+
+// out[m, :] = x[m, :] / sqrt(mean(x^2) + eps) * (offset + w)
+template <typename T>
+__global__ void norm_f32_kernel(const float* __restrict__ x, const T* __restrict__ w, T* __restrict__ out, int W, float eps,
+                                float offset) {
+  __shared__ float red[33];
+  const float* xr = x + (size_t)blockIdx.x * W;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+  const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    out[(size_t)blockIdx.x * W + i] = from_f<T>(xr[i] * r * (offset + to_f(w[i])));
+}
+
+// x[m, :] += norm(y[m, :]) * (offset + w_post);  if w_next: h[m, :] = norm(x[m, :]) * (offset + w_next)
+template <typename T>
+__global__ void postnorm_add_kernel(const float* __restrict__ y, int ldy, const T* __restrict__ w_post, float* __restrict__ x,
+                                    const T* __restrict__ w_next, T* __restrict__ h, int W, float eps, float offset) {
+  __shared__ float red[33];
+  const float* yr = y + (size_t)blockIdx.x * ldy;
+  float* xr = x + (size_t)blockIdx.x * W;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) { float v = yr[i]; ss += v * v; }
+  const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
+  float s2 = 0.0f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = xr[i] + yr[i] * r * (offset + to_f(w_post[i]));
+    xr[i] = v;
+    s2 += v * v;
+  }
+  if (w_next == nullptr) return;
+  const float r2 = 1.0f / sqrtf(block_sum(s2, red) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x)          // each thread re-reads the elements it wrote itself
+    h[(size_t)blockIdx.x * W + i] = from_f<T>(xr[i] * r2 * (offset + to_f(w_next[i])));
+}
+
+// One warp per (token, head): out = o / sqrt(mean_v(o^2) + eps) * w[v] * act(gate)
+template <typename T>
+__global__ void headnorm_gate_kernel(const float* __restrict__ o, const T* __restrict__ w, const float* __restrict__ gate,
+                                     int ldg, T* __restrict__ out, int M, int H, int V, float eps, int gate_act) {
+  const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (wid >= M * H) return;
+  const int m = wid / H, hh = wid % H;
+  const float* orow = o + ((size_t)m * H + hh) * V;
+  float ss = 0.0f;
+  for (int i = lane; i < V; i += 32) { float v = orow[i]; ss += v * v; }
+  const float r = 1.0f / sqrtf(warp_sum(ss) / (float)V + eps);
+  const float* grow = gate + (size_t)m * ldg + (size_t)hh * V;
+  for (int i = lane; i < V; i += 32)
+    out[((size_t)m * H + hh) * V + i] = from_f<T>(orow[i] * r * to_f(w[i]) * apply_act(grow[i], gate_act, 0.f, 0.f));
+}
+
+// out[m, n] = act(in[m, n]) for an fp32 [M, N] block with row pitch ldi; out has pitch ldo (may alias in for OutT = float)
+template <typename OutT>
+__global__ void act_cast_kernel(const float* __restrict__ in, int ldi, OutT* __restrict__ out, int ldo, int M, int N, int act,
+                                float p0, float p1) {
+  const size_t total = (size_t)M * N;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = idx / N, n = idx % N;
+    out[m * ldo + n] = from_f<OutT>(apply_act(in[m * ldi + n], act, p0, p1));
+  }
+}
+
+}  // namespace jl
+
+using namespace jl;
+
+extern "C" JL_API int jl_embed_f32(const int* ids, const void* table, float* out, int M, int W, int V, int dtype, void* stream) {
+  JL_CHECK_ARG(M >= 1 && W >= 1 && V >= 1, "jl_embed_f32: bad shape M=%d W=%d V=%d", M, W, V);
+  count_launch();
+  JL_DISPATCH_DTYPE(dtype, embed_f32_kernel<T><<<M, 128, 0, (cudaStream_t)stream>>>(ids, (const T*)table, out, W, V));
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+extern "C" JL_API int jl_norm_f32(const float* x, const void* w, void* out, int M, int W, float eps, float offset, int dtype,
+                                  void* stream) {
+  JL_CHECK_ARG(M >= 1 && W >= 1, "jl_norm_f32: bad shape M=%d W=%d", M, W);
+  count_launch();
+  JL_DISPATCH_DTYPE(dtype, norm_f32_kernel<T><<<M, 256, 0, (cudaStream_t)stream>>>(x, (const T*)w, (T*)out, W, eps, offset));
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+extern "C" JL_API int jl_postnorm_add(const float* y, int ldy, const void* w_post, float* x, const void* w_next, void* h, int M,
+                                      int W, float eps, float offset, int dtype, void* stream) {
+  JL_CHECK_ARG(M >= 1 && W >= 1 && ldy >= W, "jl_postnorm_add: bad shape M=%d W=%d ldy=%d", M, W, ldy);
+  JL_CHECK_ARG((w_next == nullptr) == (h == nullptr), "jl_postnorm_add: w_next and h come together");
+  count_launch();
+  JL_DISPATCH_DTYPE(dtype, postnorm_add_kernel<T><<<M, 256, 0, (cudaStream_t)stream>>>(y, ldy, (const T*)w_post, x,
+                                                                                        (const T*)w_next, (T*)h, W, eps, offset));
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+extern "C" JL_API int jl_headnorm_gate(const float* o, const void* w, const float* gate, int ldg, void* out, int M, int H, int V,
+                                       float eps, int gate_act, int dtype, void* stream) {
+  JL_CHECK_ARG(M >= 1 && H >= 1 && V >= 1, "jl_headnorm_gate: bad shape M=%d H=%d V=%d", M, H, V);
+  const int warps = 4, blocks = (M * H + warps - 1) / warps;
+  count_launch();
+  JL_DISPATCH_DTYPE(dtype, headnorm_gate_kernel<T><<<blocks, warps * 32, 0, (cudaStream_t)stream>>>(
+                               o, (const T*)w, gate, ldg, (T*)out, M, H, V, eps, gate_act));
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+extern "C" JL_API int jl_act_cast(const float* in, int ldi, void* out, int ldo, int M, int N, int act, float p0, float p1,
+                                  int out_dtype, void* stream) {
+  JL_CHECK_ARG(M >= 1 && N >= 1 && ldi >= N && ldo >= N, "jl_act_cast: bad shape M=%d N=%d ldi=%d ldo=%d", M, N, ldi, ldo);
+  const size_t total = (size_t)M * N;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  count_launch();
+  JL_DISPATCH_DTYPE(out_dtype, act_cast_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>(in, ldi, (T*)out, ldo, M, N, act, p0, p1));
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}

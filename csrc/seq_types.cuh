@@ -1,0 +1,55 @@
+// Element-type plumbing of the kernels that run in either bfloat16 or true float32 (the hybrid
+// attention / linear-recurrence models).  dtype codes of the C ABI: 0 = bfloat16, 1 = float32.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace jl {
+
+enum { DT_BF16 = 0, DT_F32 = 1 };
+// epilogue / activation codes shared by the generic linears and jl_act_cast
+enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SCALE_SOFTCAP = 4 };
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// exact-math activations (this file's users are compiled without fast-math)
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float apply_act(float z, int act, float p0, float p1) {
+  switch (act) {
+    case ACT_RELU2: { float r = fmaxf(z, 0.0f); return r * r; }
+    case ACT_GELU_TANH: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    case ACT_SILU: return z * sigmoid_f(z);
+    case ACT_SCALE_SOFTCAP: { float s = z * p0; return p1 > 0.0f ? p1 * tanhf(s / p1) : s; }
+    default: return z;
+  }
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats of shared memory */) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();                      // red may still be read from a previous call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.0f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+#define JL_DISPATCH_DTYPE(dt, ...)                                   \
+  do {                                                               \
+    if ((dt) == jl::DT_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else { using T = float; __VA_ARGS__; }                           \
+  } while (0)
+
+}  // namespace jl

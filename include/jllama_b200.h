@@ -259,6 +259,44 @@ int jl_rs_reduce_mm(void* x, const void* part_mc, const void* norm_w, void* xn_m
  * are NCCL calls emitted by XLA for partition.py:62-78; these instructions are what the fused kernels use instead. */
 int jl_nvls_selftest(void* mc, const void* src, void* out, int n, int op, unsigned int tag, void* stream);
 
+/* ---- Kernels of the hybrid decoder family (softmax attention and linear-recurrence mixers over an fp32 residual
+ * stream).  `dtype` 0 = bfloat16, 1 = true float32 (operands, cache and outputs; statistics and sums are fp32 in both).
+ * These designs have no counterpart in the reference; the mechanisms are described at the kernels. */
+
+/* ids int32 [M]; table [V, W] of dtype; out fp32 [M, W]. */
+int jl_embed_f32(const int* ids, const void* table, float* out, int M, int W, int V, int dtype, void* stream);
+/* out[m] = x[m] / sqrt(mean(x[m]^2) + eps) * (offset + w); x fp32 [M, W]; w, out of dtype. */
+int jl_norm_f32(const float* x, const void* w, void* out, int M, int W, float eps, float offset, int dtype, void* stream);
+/* x[m] += norm(y[m]) * (offset + w_post) with y fp32 [M, W] (row pitch ldy); if w_next: h[m] = norm(x[m]) * (offset + w_next). */
+int jl_postnorm_add(const float* y, int ldy, const void* w_post, float* x, const void* w_next, void* h, int M, int W, float eps,
+                    float offset, int dtype, void* stream);
+/* out[m, h, :] = o[m, h, :] / rms * w[:] * act(gate[m, h*V + :]); o fp32 [M, H, V]; gate fp32 with row pitch ldg. */
+int jl_headnorm_gate(const float* o, const void* w, const float* gate, int ldg, void* out, int M, int H, int V, float eps,
+                     int gate_act, int dtype, void* stream);
+/* out = act(in) for an fp32 [M, N] block (pitch ldi) into out_dtype (pitch ldo).  act: 0 none, 1 relu^2, 2 gelu (tanh form),
+ * 3 silu, 4 scale by p0 then soft cap p1 * tanh(. / p1) (p1 <= 0: no cap). */
+int jl_act_cast(const float* in, int ldi, void* out, int ldo, int M, int N, int act, float p0, float p1, int out_dtype,
+                void* stream);
+/* out[:, 0:N] (pitch ldo; fp32 if out_f32 else dtype) = act(x W^T): x [M, K] (pitch ldx), W [N, K]; any M, N, K. */
+int jl_linear_any(const void* x, int ldx, const void* w, void* out, int ldo, int M, int N, int K, int act, float p0, float p1,
+                  int dtype, int out_f32, void* stream);
+/* Rotary embedding (first `rot` channels, interleaved pairs), optional unit-RMS per head, cache append.  y fp32 [B*S, ldy] holds
+ * q at q_off ([H*D]), k at k_off ([G*D]; < 0: queries only), v at v_off ([G*Dv]); caches [B][G][T_cap][D|Dv] of dtype. */
+int jl_attn_prep(const float* y, int ldy, int q_off, int k_off, int v_off, void* q_out, void* k_cache, void* v_cache,
+                 const float* cos_t, const float* sin_t, int max_pos, int rot, int unit_norm, float eps, const int* cache_len,
+                 const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int dtype, void* stream);
+/* Causal softmax attention of S new tokens per row (slots *cache_len .. *cache_len+S-1) over slots [pad_left[b], own slot];
+ * q [B*S, H, D], out [B*S, H, Dv]; gate (optional) fp32 [B*S, ldg], column h: out *= sigmoid(gate). */
+int jl_attn_generic(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
+                    const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, float scale,
+                    int dtype, void* stream);
+/* out[m, h, :] *= sigmoid(gate[m, h]) in place. */
+int jl_head_gate(void* out, const float* gate, int ldg, int M, int H, int Dv, int dtype, void* stream);
+/* Gated linear attention scan: state [B][H][D][Dv] fp32 (in/out), o fp32 [B*S, H, Dv]; a2 [H*D, R], a2_bias [H*D] of dtype. */
+int jl_gla_scan(const float* y, int ldy, int q_off, int k_off, int v_off, int a_off, const void* a2, const void* a2_bias,
+                float* state, float* o, const int* cache_len, const int* pad_left, int B, int S, int H, int D, int Dv, int R,
+                float q_scale, float tau, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -239,3 +239,153 @@ def preset(name: str, **overrides: Any) -> LLaMAConfig:
     kw = dict(PRESETS[name])
     kw.update(overrides)
     return LLaMAConfig(**kw)
+
+
+# --------------------------------------------------------------------------- hybrid decoder family
+@dataclass
+class RotarySpec:
+    """Interleaved-pair rotary embedding on the first `dims` channels of each head, frequencies base^(-2i/dims)."""
+    dims: int
+    base: float
+
+
+@dataclass
+class AttentionMixerSpec:
+    """Softmax attention mixer.  `kv_from` names the layer whose cached keys / values this layer reads instead of
+    projecting its own.  qk_unit_norm: weight-free unit-RMS scaling of q and k per head after the rotation;
+    head_gate: one sigmoid gate per head on the output."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: Optional[RotarySpec] = None
+    kv_from: Optional[int] = None
+    qk_unit_norm: bool = True
+    head_gate: bool = True
+    kind: str = "attention"
+
+
+@dataclass
+class GlaMixerSpec:
+    """Gated linear attention mixer: per-head matrix state [dim x vdim], per-key-channel decay sigmoid(z)^(1/tau)."""
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+    kind: str = "gla"
+
+
+@dataclass
+class DenseMlpSpec:
+    ff: int
+    act: str = "relu2"
+    kind: str = "dense"
+
+
+@dataclass
+class HybridLayerSpec:
+    mixer: Any
+    mlp: Optional[DenseMlpSpec]
+
+
+class FoliraxConfig:
+    """Folirax: a decoder whose layers mix gated linear attention and softmax attention (rotary on part of each head,
+    unit-norm q / k, per-head output gates, layers that share another layer's keys and values), every sublayer wrapped
+    in a zero-centred RMS norm before and after, squared-ReLU feed-forward, scaled and soft-capped logits.
+
+    The JSON schema is the checkpoint's ``config.json``: ``architecture``, ``vocab``, ``width``, ``norm.eps``,
+    ``logit_scale``, ``logit_softcap`` and ``layers`` — a list of ``{"type", "mixer": {...}, "mlp": {...} | null}``.
+    """
+
+    model_type = "folirax"
+    architecture = "Folirax"
+
+    def __init__(self, vocab: int, width: int, layers: Any, norm: Optional[Dict[str, Any]] = None,
+                 logit_scale: float = 1.0, logit_softcap: Optional[float] = None, **extra: Any):
+        self.vocab_size = int(vocab)
+        self.hidden_size = int(width)
+        self.rms_norm_eps = float((norm or {}).get("eps", 1e-6))
+        self.logit_scale = float(logit_scale)
+        self.logit_softcap = float(logit_softcap) if logit_softcap else 0.0
+        self.layer_dicts = copy.deepcopy(list(layers))
+        self.layers = [self._parse_layer(i, d) for i, d in enumerate(self.layer_dicts)]
+        self.extra = {k: v for k, v in extra.items() if k != "architecture"}
+        # generation defaults the front-end reads from every config
+        self.pad_token_id, self.bos_token_id, self.eos_token_id = 0, -1, -1
+        self.validate()
+
+    @staticmethod
+    def _parse_layer(i: int, d: Dict[str, Any]) -> HybridLayerSpec:
+        m = d["mixer"]
+        kind = d["type"]
+        if kind == "gla":
+            mixer: Any = GlaMixerSpec(heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), tau=float(m["tau"]))
+        elif kind == "attention":
+            rot = m.get("rot")
+            mixer = AttentionMixerSpec(
+                heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                scale=float(m["scale"]), rot=RotarySpec(int(rot["dims"]), float(rot["base"])) if rot else None,
+                kv_from=None if m.get("kv_from") is None else int(m["kv_from"]))
+        else:
+            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        mlp = d.get("mlp")
+        spec = None
+        if mlp is not None:
+            if mlp.get("kind", "dense") != "dense":
+                raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+            spec = DenseMlpSpec(ff=int(mlp["ff"]), act=str(mlp.get("act", "relu2")))
+        return HybridLayerSpec(mixer=mixer, mlp=spec)
+
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.layers)
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.hidden_size <= 0 or not self.layers:
+            raise ValueError("vocab, width and layers must be non-empty")
+        for i, l in enumerate(self.layers):
+            m = l.mixer
+            if m.kind == "attention":
+                if m.heads % m.kv_heads:
+                    raise ValueError(f"layer {i}: heads {m.heads} not a multiple of kv_heads {m.kv_heads}")
+                if m.rot is not None and (m.rot.dims % 2 or m.rot.dims > m.dim):
+                    raise ValueError(f"layer {i}: rot.dims {m.rot.dims} must be even and at most dim {m.dim}")
+                if m.kv_from is not None:
+                    if not 0 <= m.kv_from < i:
+                        raise ValueError(f"layer {i}: kv_from {m.kv_from} must name an earlier layer")
+                    src = self.layers[m.kv_from].mixer
+                    if src.kind != "attention" or src.kv_from is not None:
+                        raise ValueError(f"layer {i}: kv_from {m.kv_from} is not an attention layer with its own keys")
+                    if (src.kv_heads, src.dim, src.vdim) != (m.kv_heads, m.dim, m.vdim):
+                        raise ValueError(f"layer {i}: key / value sizes differ from layer {m.kv_from}")
+            elif m.tau <= 0:
+                raise ValueError(f"layer {i}: tau must be positive")
+
+    def to_dict(self) -> Dict[str, Any]:
+        d: Dict[str, Any] = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+                             "norm": {"eps": self.rms_norm_eps}, "logit_scale": self.logit_scale,
+                             "logit_softcap": self.logit_softcap, "layers": copy.deepcopy(self.layer_dicts)}
+        d.update(self.extra)
+        return d
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "FoliraxConfig":
+        return cls(**d)
+
+    @classmethod
+    def from_json_file(cls, path: str) -> "FoliraxConfig":
+        with open(path) as f:
+            return cls.from_dict(json.load(f))
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "FoliraxConfig":
+        return cls.from_json_file(os.path.join(path, CONFIG_NAME) if os.path.isdir(path) else path)
+
+    def save_pretrained(self, save_directory: str) -> None:
+        os.makedirs(save_directory, exist_ok=True)
+        with open(os.path.join(save_directory, CONFIG_NAME), "w") as f:
+            json.dump(self.to_dict(), f, indent=1, sort_keys=True)
+
+    def __repr__(self) -> str:
+        return f"FoliraxConfig {json.dumps(self.to_dict(), sort_keys=True)}"

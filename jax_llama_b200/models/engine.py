@@ -44,6 +44,11 @@ class DeviceKVCache(KVCache):
         self.index = int(value)
         self.len_dev.fill_(int(value))
 
+    def mutable_state(self) -> List[torch.Tensor]:
+        """Tensors a decode step changes besides the appended slots (saved and restored around the warm-up and the
+        capture of a decode graph).  Caches that also carry recurrent state add it here."""
+        return [self.len_dev]
+
 
 @dataclass
 class LayerWeights:
@@ -494,7 +499,10 @@ class B200Engine:
     @torch.no_grad()
     def forward(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
                 position_ids: Optional[torch.Tensor] = None, cache: Optional[DeviceKVCache] = None,
-                with_head: bool = True, last_only: bool = False, gather_logits: bool = True) -> ModelOutput:
+                with_head: bool = True, last_only: bool = False, gather_logits: bool = True,
+                logit_rows: Optional[torch.Tensor] = None) -> ModelOutput:
+        """`logit_rows`: flat indices into the [B·S] token rows; the head then runs on those rows only and `.logits`
+        is [len(logit_rows), V] (single GPU)."""
         B, S = input_ids.shape
         c = self.config
         own_cache = cache is None
@@ -528,7 +536,7 @@ class B200Engine:
             return out
         if self.comm is not None:
             self.comm.begin_sequence()
-        x = K.embed(input_ids.reshape(-1), self.embedding)
+        x = self._embed(input_ids.reshape(-1))
         x = self._layers(x, B, S, cache, positions)
         if self.comm is not None:
             self.comm.end_sequence()
@@ -536,13 +544,19 @@ class B200Engine:
                 self.comm.nvls_end_forward()        # in-switch all-reduces of this forward: advance their epoch base
         cache.set_index(cache.index + S)
         out = ModelOutput(past_key_values=None if own_cache else cache)
+        if logit_rows is not None:
+            if self.tp > 1 or not with_head:
+                raise NotImplementedError("logit_rows is a single-GPU option of the causal-LM forward")
+            rows_x = x.index_select(0, logit_rows.to(device=x.device, dtype=torch.long)).contiguous()
+            out.logits = self._head(rows_x)
+            return out
         if last_only:
             x = x.view(B, S, c.hidden_size)[:, -1].contiguous()
             rows = 1
         else:
             rows = S
         if with_head:
-            logits = K.linear(x, self.lm_head, norm_w=self.final_norm, eps=c.rms_norm_eps, out_f32=True)
+            logits = self._head(x)
             if self.tp > 1 and gather_logits:
                 # API parity: `.logits` is the full vocabulary.  This gather is off the generate() path,
                 # which exchanges only top-k candidates (see _select_and_advance).
@@ -555,6 +569,27 @@ class B200Engine:
         else:
             out.last_hidden_state = K.rmsnorm(x, self.final_norm, c.rms_norm_eps).view(B, rows, c.hidden_size)
         return out
+
+    # ------------------------------------------------------------------ model-specific ends of the layer stack
+    def _embed(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Token ids [M] → residual-stream rows [M, H] (the dtype the layer stack of this engine carries)."""
+        return K.embed(ids, self.embedding, out=out)
+
+    def _head(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Residual-stream rows → fp32 logits over this rank's vocabulary shard: final norm + LM head."""
+        return K.linear(x, self.lm_head, norm_w=self.final_norm, eps=self.config.rms_norm_eps, out_f32=True, out=out)
+
+    def _check_max_length(self, max_length: int) -> None:
+        if max_length > 2 * self.config.max_sequence_length:
+            raise ValueError(f"max_length {max_length} exceeds the rotary table (2 x max_sequence_length)")
+
+    def release_state(self, st: DecodeState) -> None:
+        """Give back what a finished request batch holds: its decode buffers, cache (and recurrent state) and graphs."""
+        for key, val in list(self._decode_states.items()):
+            if val is st:
+                del self._decode_states[key]
+        st.graphs.clear()
+        st._cache = None
 
     # ------------------------------------------------------------------ decode state + graph
     def _decode_state(self, B: int, max_len: int) -> DecodeState:
@@ -684,12 +719,12 @@ class B200Engine:
                 self.comm.end_sequence()
             return
         else:
-            K.embed(st.ids, self.embedding, out=st.x)
+            self._embed(st.ids, out=st.x)
             x = self._layers(st.x, st.B, 1, cache, None, ws=st)
             if getattr(st, "xn_final", None) is not None:
                 K.linear(st.xn_final, self.lm_head, out_f32=True, out=st.logits)
             else:
-                K.linear(x, self.lm_head, norm_w=self.final_norm, eps=c.rms_norm_eps, out_f32=True, out=st.logits)
+                self._head(x, out=st.logits)
         self._select_and_advance(st, cache, sampling, eos, pad)
         if self.comm is not None:
             self.comm.end_sequence()
@@ -705,21 +740,21 @@ class B200Engine:
             return st.graphs[key]
         # warm up outside capture on a side stream (first-use initialisation, cudaFuncSetAttribute, …);
         # the step is re-playable because a snapshot of the mutable state is restored afterwards
-        snap = [t.clone() for t in (st.ids, st.finished, st.sequences, st.cur_len, st.step, st.n_unfinished,
-                                    cache.len_dev)]
+        mutable = (st.ids, st.finished, st.sequences, st.cur_len, st.step, st.n_unfinished, *cache.mutable_state())
+        snap = [t.clone() for t in mutable]
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             self._decode_step(st, cache, sampling, eos, pad)
         torch.cuda.current_stream().wait_stream(side)
-        for t, s in zip((st.ids, st.finished, st.sequences, st.cur_len, st.step, st.n_unfinished, cache.len_dev), snap):
+        for t, s in zip(mutable, snap):
             t.copy_(s)
         g = torch.cuda.CUDAGraph()
         n0 = _lib.launch_count()
         with torch.cuda.graph(g):
             self._decode_step(st, cache, sampling, eos, pad)
         st.kernels_per_step = _lib.launch_count() - n0      # kernel nodes in the captured step
-        for t, s in zip((st.ids, st.finished, st.sequences, st.cur_len, st.step, st.n_unfinished, cache.len_dev), snap):
+        for t, s in zip(mutable, snap):
             t.copy_(s)
         st.graphs[key] = g
         return g
@@ -736,8 +771,7 @@ class B200Engine:
                  seed: int = 0, check_every: int = 16) -> torch.Tensor:
         """Prefill + graph-replayed decode.  Returns [B, max_length] int64 (pad-filled), like HF generate."""
         B, S = input_ids.shape
-        if max_length > 2 * self.config.max_sequence_length:
-            raise ValueError(f"max_length {max_length} exceeds the rotary table (2 x max_sequence_length)")
+        self._check_max_length(max_length)
         from ..utils.stats import CudaTimer, GenerationStats, nvtx_range
         st = self._decode_state(B, max_length)
         stats = GenerationStats(batch=B, prompt_len=S, weight_bytes_per_step=self.weight_bytes_per_step())
@@ -775,8 +809,9 @@ class B200Engine:
         return sum(t.numel() * 2 for t in (self.wqkv_all, self.wo_all, self.w13_all, self.w2_all, self.lm_head))
 
     def prepare(self, st: DecodeState, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor],
-                pad: int) -> DeviceKVCache:
-        """Reset the decode state for a new request batch and run the prefill."""
+                pad: int, logit_rows: Optional[torch.Tensor] = None) -> DeviceKVCache:
+        """Reset the decode state for a new request batch and run the prefill.  With `logit_rows` (flat indices into
+        the [B·S] prompt rows) the logits of those rows are kept in ``st.prompt_logits`` as well."""
         B, S = input_ids.shape
         cache = getattr(st, "_cache", None)
         if cache is None:
@@ -789,6 +824,14 @@ class B200Engine:
         st.cur_len.fill_(S)
         st.step.zero_()
         st.n_unfinished.fill_(B)
+        if logit_rows is not None:
+            last = torch.arange(B, device=self.device) * S + (S - 1)
+            rows = torch.cat([logit_rows.to(device=self.device, dtype=torch.long).reshape(-1), last])
+            out = self.forward(input_ids, attention_mask=attention_mask, cache=cache, logit_rows=rows)
+            st.prompt_logits = out.logits[:rows.numel() - B]
+            st.logits.copy_(out.logits[rows.numel() - B:])
+            return cache
+        st.prompt_logits = None
         out = self.forward(input_ids, attention_mask=attention_mask, cache=cache, last_only=True, gather_logits=False)
         st.logits.copy_(out.logits.view(B, -1))
         return cache
@@ -809,11 +852,13 @@ class B200Engine:
     def begin_stream(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None, *,
                      max_length: int, do_sample: bool = False, temperature: float = 1.0,
                      top_k: Optional[int] = 50, top_p: float = 1.0, pad_token_id: int = 0,
-                     eos_token_id: int = -1, seed: int = 0) -> "EngineStream":
-        """Prefill and select the first new token; subsequent tokens come from `EngineStream.step`."""
+                     eos_token_id: int = -1, seed: int = 0, logit_rows: Optional[torch.Tensor] = None) -> "EngineStream":
+        """Prefill and select the first new token; subsequent tokens come from `EngineStream.step`.  `logit_rows`:
+        prompt rows whose logits the caller wants to read back (`EngineStream.prompt_logits`)."""
         B, S = input_ids.shape
+        self._check_max_length(max_length)
         st = self._decode_state(B, max_length)
-        cache = self.prepare(st, input_ids, attention_mask, pad_token_id)
+        cache = self.prepare(st, input_ids, attention_mask, pad_token_id, logit_rows=logit_rows)
         sampling = (bool(do_sample), float(temperature), int(top_k or 0), float(top_p), int(seed))
         self._select_and_advance_after_prefill(st, cache, sampling, eos_token_id, pad_token_id)
         graph = self._graph_for(st, cache, sampling, eos_token_id, pad_token_id)
@@ -855,3 +900,16 @@ class EngineStream:
 
     def sequences(self) -> torch.Tensor:
         return self.st.sequences[:, :self.length].to(torch.long)
+
+    def logits(self) -> torch.Tensor:
+        """fp32 [B, V] logits of the most recent step (after the prefill: of the last prompt position)."""
+        return self.st.logits
+
+    def prompt_logits(self) -> Optional[torch.Tensor]:
+        """fp32 logits of the prompt rows asked for with `logit_rows` at `begin_stream`."""
+        return getattr(self.st, "prompt_logits", None)
+
+    def close(self) -> None:
+        """The request batch is over: its cache, recurrent state, buffers and graphs go back to the allocator."""
+        self.engine.release_state(self.st)
+        self.graph = None

@@ -1,0 +1,280 @@
+"""Engine of the hybrid decoder family: layers that mix softmax attention and linear-recurrence mixers over an fp32
+residual stream, each sublayer between two RMS norms.
+
+It is the B200 engine (`models/engine.py`) with another layer stack: the request batching (left-padded static batch),
+the decode state, on-device selection and bookkeeping, CUDA-graph replay of the decode step, `generate` and the
+token-at-a-time stream are inherited; what changes is
+
+* the weights (per-layer mixers from `models/mixers.py`, dense feed-forward, zero-centred norm weights),
+* the cache: per attention layer a key / value cache with that layer's head sizes (none for a layer that reads another
+  layer's), per recurrent layer an fp32 state, all advanced by the same device-side fill level and left-pad counts,
+* the numerics: norms, softmax, recurrences and the residual sum in fp32; matrix operands in bfloat16, or everything in
+  true float32 (`dtype=torch.float32`), which the kernels of this family are built for.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from ..ops import _lib
+from ..ops import kernels as K
+from ..ops import seq_kernels as SK
+from .engine import B200Engine, DecodeState, DeviceKVCache
+from .mixers import MIXERS, rotary_table
+
+
+@dataclass
+class HybridCache(DeviceKVCache):
+    """Per-layer caches of unequal shapes plus recurrent states.  `k` / `v` of the base class point at the first
+    attention layer's tensors (identity of the cache for graph keys)."""
+
+    ks: List[Optional[torch.Tensor]] = field(default_factory=list)
+    vs: List[Optional[torch.Tensor]] = field(default_factory=list)
+    states: List[Optional[torch.Tensor]] = field(default_factory=list)
+    length: int = 0
+
+    @property
+    def capacity(self) -> int:
+        return self.length
+
+    def set_index(self, value: int) -> None:
+        super().set_index(value)
+        if int(value) == 0:                       # a new request batch starts from an empty state
+            for s in self.states:
+                if s is not None:
+                    s.zero_()
+
+    def mutable_state(self) -> List[torch.Tensor]:
+        return [self.len_dev] + [s for s in self.states if s is not None]
+
+
+@dataclass
+class HybridLayer:
+    mixer: Any
+    norm1: torch.Tensor
+    norm1b: torch.Tensor
+    norm2: Optional[torch.Tensor] = None
+    norm2b: Optional[torch.Tensor] = None
+    up: Optional[torch.Tensor] = None
+    down: Optional[torch.Tensor] = None
+    act: int = SK.ACT_RELU2
+
+
+def tensor_shapes(config: Any, decay_rank: int = 16) -> Dict[str, Tuple[int, ...]]:
+    """Checkpoint tensor names → shapes for a config of this family (what a loader expects, what random_init draws).
+    The rank of the decay projection is not a config key: a checkpoint fixes it by the shape of ``mix.a1``."""
+    W = config.hidden_size
+    out: Dict[str, Tuple[int, ...]] = {"embed": (config.vocab_size, W), "final.norm": (W,), "head": (config.vocab_size, W)}
+    for i, l in enumerate(config.layers):
+        p, m = f"l{i}.", l.mixer
+        out[p + "norm1"], out[p + "norm1b"] = (W,), (W,)
+        if m.kind == "gla":
+            out.update({p + "mix.q": (m.heads * m.dim, W), p + "mix.k": (m.heads * m.dim, W),
+                        p + "mix.v": (m.heads * m.vdim, W), p + "mix.g": (m.heads * m.vdim, W),
+                        p + "mix.o": (W, m.heads * m.vdim), p + "mix.norm": (m.vdim,), p + "mix.a1": (decay_rank, W),
+                        p + "mix.a2": (m.heads * m.dim, decay_rank), p + "mix.a2.b": (m.heads * m.dim,)})
+        else:
+            out[p + "mix.q"] = (m.heads * m.dim, W)
+            if m.kv_from is None:
+                out[p + "mix.k"], out[p + "mix.v"] = (m.kv_heads * m.dim, W), (m.kv_heads * m.vdim, W)
+            if m.head_gate:
+                out[p + "mix.g"] = (m.heads, W)
+            out[p + "mix.o"] = (W, m.heads * m.vdim)
+        if l.mlp is not None:
+            out.update({p + "norm2": (W,), p + "norm2b": (W,), p + "mlp.up": (l.mlp.ff, W), p + "mlp.down": (W, l.mlp.ff)})
+    return out
+
+
+class HybridEngine(B200Engine):
+    norm_offset = 1.0          # norm weights are stored around zero
+
+    def __init__(self, config: Any, tensors: Dict[str, torch.Tensor], *, dtype: torch.dtype = torch.bfloat16,
+                 device: Any = "cuda", use_cuda_graph: bool = True):
+        """`tensors`: checkpoint names → tensors (any float dtype, any device); they are cast to `dtype` and moved."""
+        self.config = config
+        self.dtype = dtype
+        SK.dtype_code(dtype)
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise ValueError("HybridEngine needs a CUDA device (there is no CPU path for this family)")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        _lib.lib()
+        self.tp, self.rank, self.comm = 1, 0, None
+        self.use_cuda_graph = use_cuda_graph
+        self.use_megakernel = False
+        self.mega_write_logits = False
+        self.mega_max_batch = 0
+        self.eps = float(config.rms_norm_eps)
+        want = None
+        for name, t in tensors.items():
+            if name.endswith("mix.a1"):
+                want = tensor_shapes(config, decay_rank=int(t.shape[0]))
+                break
+        want = want or tensor_shapes(config)
+        missing = sorted(set(want) - set(tensors))
+        if missing:
+            raise ValueError(f"checkpoint lacks tensors: {missing[:8]}{' ...' if len(missing) > 8 else ''}")
+        for name, shape in want.items():
+            if tuple(tensors[name].shape) != tuple(shape):
+                raise ValueError(f"tensor {name}: shape {tuple(tensors[name].shape)}, config wants {tuple(shape)}")
+
+        def get(name: str) -> torch.Tensor:
+            return tensors[name].to(device=self.device, dtype=dtype).contiguous()
+
+        self.embedding = get("embed")
+        self.final_norm = get("final.norm")
+        self.lm_head = get("head")
+        self.v_local = config.vocab_size
+        self.layers: List[HybridLayer] = []
+        for i, l in enumerate(config.layers):
+            p = f"l{i}."
+            w = {k[len(p) + 4:]: get(k) for k in want if k.startswith(p + "mix.")}
+            layer = HybridLayer(mixer=MIXERS[l.mixer.kind](l.mixer, w, self.eps), norm1=get(p + "norm1"),
+                                norm1b=get(p + "norm1b"))
+            if l.mlp is not None:
+                if l.mlp.act not in SK.ACTIVATIONS:
+                    raise ValueError(f"layer {i}: unknown activation {l.mlp.act!r}")
+                layer.norm2, layer.norm2b = get(p + "norm2"), get(p + "norm2b")
+                layer.up, layer.down, layer.act = get(p + "mlp.up"), get(p + "mlp.down"), SK.ACTIVATIONS[l.mlp.act]
+            self.layers.append(layer)
+        self._rope: Dict[Tuple[int, float], Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._decode_states: Dict[Tuple[int, int], DecodeState] = {}
+        self._mega_gen = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._mega_fit_cache: Dict[int, bool] = {}
+        self.capture_streams: Optional[List[torch.Tensor]] = None      # debugging: residual stream after every layer
+        if dtype == torch.bfloat16:
+            K.ensure_gemm_workspace(self.device)
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def random_init(cls, config: Any, device: Any = "cuda", seed: int = 0, dtype: torch.dtype = torch.bfloat16,
+                    decay_rank: int = 16, **kw: Any) -> "HybridEngine":
+        """Random weights in checkpoint layout, drawn on the device (benchmarks and tests)."""
+        return cls(config, random_tensors(config, device, seed, decay_rank), dtype=dtype, device=device, **kw)
+
+    def _mega_fits(self, batch: int) -> bool:
+        return False
+
+    def weight_bytes_per_step(self) -> int:
+        ws = [self.lm_head, self.final_norm]
+        for l in self.layers:
+            ws += l.mixer.weights() + [t for t in (l.norm1, l.norm1b, l.norm2, l.norm2b, l.up, l.down) if t is not None]
+        return sum(t.numel() * t.element_size() for t in ws)
+
+    # ------------------------------------------------------------------ rotary tables
+    def _rope_for(self, dims: int, base: float, length: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        key = (int(dims), float(base))
+        have = self._rope.get(key)
+        if have is None or have[0].shape[0] < length:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("rotary table too short for a captured step: size it before the capture")
+            self._rope[key] = have = rotary_table(dims, base, max(length, 256), self.device)
+        return have
+
+    def _check_max_length(self, max_length: int) -> None:
+        for l in self.layers:
+            s = l.mixer.spec
+            if l.mixer.kind == "attention" and s.rot is not None:
+                self._rope_for(s.rot.dims, s.rot.base, max_length)
+
+    # ------------------------------------------------------------------ cache
+    def new_cache(self, batch: int, max_length: int) -> HybridCache:
+        ks: List[Optional[torch.Tensor]] = []
+        vs: List[Optional[torch.Tensor]] = []
+        states: List[Optional[torch.Tensor]] = []
+        for l in self.layers:
+            kv = l.mixer.new_cache(batch, max_length, self.device)
+            ks.append(kv[0] if kv is not None else None)
+            vs.append(kv[1] if kv is not None else None)
+            states.append(l.mixer.new_state(batch, self.device))
+        first = next((k for k in ks if k is not None), None)
+        ident = first if first is not None else torch.zeros(1, dtype=self.dtype, device=self.device)
+        self._check_max_length(max_length)
+        return HybridCache(k=ident, v=ident, index=0,
+                           pad_left=torch.zeros(batch, dtype=torch.int32, device=self.device),
+                           len_dev=torch.zeros(1, dtype=torch.int32, device=self.device),
+                           ks=ks, vs=vs, states=states, length=int(max_length))
+
+    # ------------------------------------------------------------------ layer stack
+    def _embed(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return SK.embed_f32(ids, self.embedding, out=out)
+
+    def _head(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        c = self.config
+        h = SK.norm_f32(x, self.final_norm, self.eps, self.norm_offset)
+        return SK.linear(h, self.lm_head, act=SK.ACT_SCALE_SOFTCAP, p0=c.logit_scale, p1=c.logit_softcap, out=out)
+
+    def _layers(self, x: torch.Tensor, B: int, S: int, cache: HybridCache, positions: Optional[torch.Tensor],
+                ws: Optional[DecodeState] = None) -> torch.Tensor:
+        """x fp32 [B·S, width], updated in place through all layers.  Appends S slots at cache.len_dev and advances
+        the recurrent states by the S tokens (padding tokens excluded); does not advance the fill level."""
+        if positions is not None:
+            raise NotImplementedError("explicit position_ids are not supported by the hybrid engine (left padding is)")
+        eps, off = self.eps, self.norm_offset
+        n = len(self.layers)
+        h = SK.norm_f32(x, self.layers[0].norm1, eps, off)
+        for i, l in enumerate(self.layers):
+            rope = None
+            sp = l.mixer.spec
+            if l.mixer.kind == "attention":
+                rope = self._rope_for(sp.rot.dims, sp.rot.base, cache.capacity) if sp.rot is not None else \
+                    self._rope_for(2, 1.0, 1)
+            u = l.mixer.run(h, B, S, cache, i, rope)
+            z = SK.linear(u, l.mixer.wo)
+            nxt = l.norm2 if l.up is not None else (self.layers[i + 1].norm1 if i + 1 < n else None)
+            h = SK.postnorm_add(z, l.norm1b, x, eps, off, w_next=nxt)
+            if l.up is not None:
+                t = SK.linear(h, l.up, act=l.act, out_f32=False)
+                z = SK.linear(t, l.down)
+                nxt = self.layers[i + 1].norm1 if i + 1 < n else None
+                h = SK.postnorm_add(z, l.norm2b, x, eps, off, w_next=nxt)
+            if self.capture_streams is not None:
+                self.capture_streams.append(x.clone())
+        return x
+
+    # ------------------------------------------------------------------ decode state
+    def _decode_state(self, B: int, max_len: int) -> DecodeState:
+        key = (B, max_len)
+        if key in self._decode_states:
+            return self._decode_states[key]
+        c, dev = self.config, self.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        self._check_max_length(max_len)
+        empty = torch.zeros(1, dtype=self.dtype, device=dev)
+        st = DecodeState(
+            B=B, max_len=max_len, ids=torch.zeros(B, **i32),
+            x=torch.zeros(B, c.hidden_size, dtype=torch.float32, device=dev), qkv=empty, attn=empty, mlp=empty,
+            logits=torch.zeros(B, c.vocab_size, dtype=torch.float32, device=dev), tok=torch.zeros(B, **i32),
+            finished=torch.zeros(B, **i32), sequences=torch.zeros(B, max_len, **i32),
+            cur_len=torch.zeros(1, **i32), step=torch.zeros(1, **i32), n_unfinished=torch.zeros(1, **i32),
+            splits=1, scratch=None)
+        self._decode_states[key] = st
+        return st
+
+
+def random_tensors(config: Any, device: Any = "cuda", seed: int = 0, decay_rank: int = 16) -> Dict[str, torch.Tensor]:
+    """Random bfloat16 weights under checkpoint names: projections ~ N(0, 1/fan_in), norm weights small around zero
+    (the head norm around one), decay biases spread so that fast and slow channels both occur."""
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(int(seed))
+    out: Dict[str, torch.Tensor] = {}
+
+    def randn(shape: Tuple[int, ...]) -> torch.Tensor:
+        return torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+
+    for name, shape in tensor_shapes(config, decay_rank).items():
+        if name.endswith("mix.norm"):
+            t = 1.0 + 0.1 * randn(shape)
+        elif name.endswith("mix.a2.b"):
+            t = 2.0 + 2.0 * randn(shape)
+        elif len(shape) == 1:
+            t = 0.1 * randn(shape)
+        elif name == "embed":
+            t = randn(shape)
+        else:
+            t = randn(shape) / (shape[1] ** 0.5)
+        out[name] = t.to(torch.bfloat16)
+    return out

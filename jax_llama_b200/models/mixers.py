@@ -1,0 +1,144 @@
+"""Sequence mixers of the hybrid decoder family, each a small class over the kernels of `ops/seq_kernels.py`.
+
+A mixer owns its projection weights in kernel layout (projections that read the same input are stacked into one
+matrix, so a layer issues one GEMM for them), knows what it keeps between tokens (a key / value cache, a recurrent
+state, or nothing of its own when it reads another layer's cache) and turns the normalised input ``h [B·S, width]``
+into the input of the output projection.  Constants of a mechanism (rotary share and base, score scale, decay
+temperature, which norms and gates are on) are parameters of its spec (`config.py`), not of the code.
+
+The output projection, the norms around the sublayer and the residual sum belong to the layer stack
+(`models/hybrid_engine.py`), which is the same for every mixer.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..config import AttentionMixerSpec, GlaMixerSpec
+from ..ops import kernels as K
+from ..ops import seq_kernels as SK
+
+
+def _stack_rows(parts: List[torch.Tensor], multiple: int = 8) -> Tuple[torch.Tensor, List[int]]:
+    """Concatenate weight matrices [n_i, K] on the output axis, zero-padded to a multiple of `multiple` rows (the
+    tensor-core GEMM wants N % 8 == 0).  Returns the matrix and the first row of every part."""
+    offs, n = [], 0
+    for p in parts:
+        offs.append(n)
+        n += p.shape[0]
+    pad = (-n) % multiple
+    if pad:
+        parts = parts + [torch.zeros((pad, parts[0].shape[1]), dtype=parts[0].dtype, device=parts[0].device)]
+    return torch.cat(parts, 0).contiguous(), offs
+
+
+def rotary_table(dims: int, base: float, length: int, device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin of position · base^(-2i/dims), i < dims/2, as fp32 [length, dims/2] (angles formed in float64)."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+    ang = torch.arange(length, dtype=torch.float64)[:, None] * freq[None, :]
+    return torch.cos(ang).float().to(device).contiguous(), torch.sin(ang).float().to(device).contiguous()
+
+
+class AttentionMixer:
+    """Softmax attention: grouped key / value heads, query / key size `dim` and value size `vdim` (they may differ),
+    rotary embedding on the first `rot.dims` channels, optional unit-RMS q / k, optional sigmoid gate per head,
+    optional reuse of another layer's cache (`kv_from`)."""
+
+    kind = "attention"
+
+    def __init__(self, spec: AttentionMixerSpec, w: Dict[str, torch.Tensor], eps: float):
+        self.spec, self.eps = spec, float(eps)
+        self.shares_kv = spec.kv_from is not None
+        parts = [w["q"]] + ([] if self.shares_kv else [w["k"], w["v"]]) + ([w["g"]] if spec.head_gate else [])
+        self.w_in, offs = _stack_rows(parts)
+        self.q_off = offs[0]
+        self.k_off, self.v_off = (-1, -1) if self.shares_kv else (offs[1], offs[2])
+        self.g_off = offs[-1] if spec.head_gate else -1
+        self.wo = w["o"].contiguous()
+        self.dtype = self.wo.dtype
+
+    def weights(self) -> List[torch.Tensor]:
+        return [self.w_in, self.wo]
+
+    def new_cache(self, batch: int, length: int, device: torch.device) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        if self.shares_kv:
+            return None
+        s = self.spec
+        return (torch.zeros((batch, s.kv_heads, length, s.dim), dtype=self.dtype, device=device),
+                torch.zeros((batch, s.kv_heads, length, s.vdim), dtype=self.dtype, device=device))
+
+    def new_state(self, batch: int, device: torch.device) -> Optional[torch.Tensor]:
+        return None
+
+    def run(self, h: torch.Tensor, B: int, S: int, cache: "object", layer: int, rope: Tuple[torch.Tensor, torch.Tensor]
+            ) -> torch.Tensor:
+        s = self.spec
+        y = SK.linear(h, self.w_in)                                   # fp32 [M, q | k | v | gate]
+        q = torch.empty((B * S, s.heads * s.dim), dtype=self.dtype, device=h.device)
+        src = layer if not self.shares_kv else s.kv_from
+        kc, vc = cache.ks[src], cache.vs[src]
+        rot = s.rot.dims if s.rot is not None else 0
+        SK.attn_prep(y, self.q_off, self.k_off, self.v_off, q, None if self.shares_kv else kc,
+                     None if self.shares_kv else vc, rope[0], rope[1], rot, s.qk_unit_norm, self.eps, cache.len_dev,
+                     cache.pad_left, B, S, s.heads, s.kv_heads, s.dim, s.vdim)
+        gate = y[:, self.g_off:self.g_off + s.heads] if s.head_gate else None
+        if self._tensor_core_shape(S):
+            # 128-wide heads in bfloat16: the tcgen05 flash kernel (prompts) / the split-KV decode kernel
+            out = self._attend_tensor_cores(q, kc, vc, cache, B, S)
+            if gate is not None:
+                SK.head_gate(out.view(B * S, -1), gate, s.heads, s.vdim)
+            return out.view(B * S, s.heads * s.vdim)
+        return SK.attn_generic(q, kc, vc, gate, cache.len_dev, cache.pad_left, B, S, s.heads, s.scale)
+
+    def _tensor_core_shape(self, S: int) -> bool:
+        s = self.spec
+        return (SK.tensor_cores_enabled() and self.dtype == torch.bfloat16 and s.dim == 128 and s.vdim == 128
+                and S > 1 and abs(s.scale - 1.0 / math.sqrt(s.dim)) < 1e-12)
+
+    def _attend_tensor_cores(self, q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, cache: "object", B: int, S: int
+                             ) -> torch.Tensor:
+        s = self.spec
+        return K.prefill_attn(q.view(B, S, s.heads, s.dim), kc, vc, cache.index, S, cache.pad_left, cache.len_dev)
+
+
+class GlaMixer:
+    """Gated linear attention: S_t = diag(alpha_t) S_(t-1) + k_t v_tᵀ, o_t = S_tᵀ q_t per head, alpha from a low-rank
+    projection through sigmoid(·)^(1/tau); read-out normalised per head (plain weight shared by the heads), gated by
+    silu of a projection of the input.  The state is fp32 and is what the layer keeps between tokens."""
+
+    kind = "gla"
+
+    def __init__(self, spec: GlaMixerSpec, w: Dict[str, torch.Tensor], eps: float):
+        self.spec, self.eps = spec, float(eps)
+        self.w_in, offs = _stack_rows([w["q"], w["k"], w["v"], w["g"], w["a1"]])
+        self.q_off, self.k_off, self.v_off, self.g_off, self.a_off = offs
+        self.a2 = w["a2"].contiguous()
+        self.a2_bias = w["a2.b"].contiguous()
+        self.norm = w["norm"].contiguous()
+        self.wo = w["o"].contiguous()
+        self.dtype = self.wo.dtype
+
+    def weights(self) -> List[torch.Tensor]:
+        return [self.w_in, self.a2, self.a2_bias, self.norm, self.wo]
+
+    def new_cache(self, batch: int, length: int, device: torch.device) -> None:
+        return None
+
+    def new_state(self, batch: int, device: torch.device) -> torch.Tensor:
+        s = self.spec
+        return torch.zeros((batch, s.heads, s.dim, s.vdim), dtype=torch.float32, device=device)
+
+    def run(self, h: torch.Tensor, B: int, S: int, cache: "object", layer: int, rope: Optional[Tuple] = None
+            ) -> torch.Tensor:
+        s = self.spec
+        y = SK.linear(h, self.w_in)                                   # fp32 [M, q | k | v | gate | low-rank decay input]
+        o = SK.gla_scan(y, self.q_off, self.k_off, self.v_off, self.a_off, self.a2, self.a2_bias, cache.states[layer],
+                        cache.len_dev, cache.pad_left, B, S, s.heads, s.dim, s.vdim, s.dim ** -0.5, s.tau)
+        gate = y[:, self.g_off:self.g_off + s.heads * s.vdim]
+        return SK.headnorm_gate(o, self.norm, gate, s.heads, s.vdim, self.eps, SK.ACT_SILU)
+
+
+MIXERS = {"attention": AttentionMixer, "gla": GlaMixer}

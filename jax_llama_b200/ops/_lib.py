@@ -53,6 +53,20 @@ _SIGNATURES = {
     "jl_decode_advance": (i32, [ip, ip, ip, ip, i32, i32, i32, i32, ip, ip, ip, ip, vp]),
 }
 
+# kernels of the hybrid decoder family (csrc/seq_*.cu, attn_generic.cu, gla_scan.cu)
+_HYBRID = {
+    "jl_embed_f32": (i32, [ip, vp, fp, i32, i32, i32, i32, vp]),
+    "jl_norm_f32": (i32, [fp, vp, vp, i32, i32, f32, f32, i32, vp]),
+    "jl_postnorm_add": (i32, [fp, i32, vp, fp, vp, vp, i32, i32, f32, f32, i32, vp]),
+    "jl_headnorm_gate": (i32, [fp, vp, fp, i32, vp, i32, i32, i32, f32, i32, i32, vp]),
+    "jl_act_cast": (i32, [fp, i32, vp, i32, i32, i32, i32, f32, f32, i32, vp]),
+    "jl_linear_any": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, f32, f32, i32, i32, vp]),
+    "jl_attn_prep": (i32, [fp, i32, i32, i32, i32, vp, vp, vp, fp, fp, i32, i32, i32, f32, ip, ip] + [i32] * 8 + [vp]),
+    "jl_attn_generic": (i32, [vp, vp, vp, vp, fp, i32, ip, ip] + [i32] * 7 + [f32, i32, vp]),
+    "jl_head_gate": (i32, [vp, fp, i32, i32, i32, i32, i32, vp]),
+    "jl_gla_scan": (i32, [fp, i32, i32, i32, i32, i32, vp, vp, fp, fp, ip, ip] + [i32] * 6 + [f32, f32, i32, vp]),
+}
+
 _OPTIONAL = {
     "jl_flash_prefill_occupancy": (i32, [i32]),
     "jl_decode_mega_stages": (i32, [i32, i32, i32, i32, i32, i32]),
@@ -65,15 +79,33 @@ class NativeLibraryError(RuntimeError):
     pass
 
 
+_subset: Optional[str] = None
+
+
+def use_subset(name: str) -> None:
+    """Declare, before the first kernel call, that this process needs only the kernels of the named subset
+    (`ops/build.py` SUBSETS).  If the full library is already built and fresh it is used as always; otherwise the
+    subset's small library is built and loaded instead of the full one.  Entry points outside the subset are then
+    absent and calling them is an AttributeError, not a silent fallback."""
+    global _subset
+    if _lib is None:
+        _subset = name
+
+
 def lib() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
+    from .build import is_fresh
     path = LIB_PATH
+    partial = False
     if os.environ.get("JLLAMA_LIB"):           # A/B of two builds on one box (scripts/sweep_env.sh JLLAMA_LIB "a.so b.so")
         from pathlib import Path
         path = Path(os.environ["JLLAMA_LIB"])
-    if not path.exists():
+    elif _subset is not None and not is_fresh():
+        path, partial = build_library(subset=_subset), True
+    if not path.exists() or (path == LIB_PATH and not partial and not is_fresh()
+                             and not os.environ.get("JLLAMA_NO_AUTOBUILD")):
         if os.environ.get("JLLAMA_NO_AUTOBUILD"):
             raise NativeLibraryError(f"{path} is missing: run `python -m jax_llama_b200.ops.build`")
         build_library()
@@ -81,11 +113,11 @@ def lib() -> C.CDLL:
         handle = C.CDLL(str(path))
     except OSError as e:
         raise NativeLibraryError(f"cannot load {path}: {e}") from e
-    for name, (res, args) in {**_SIGNATURES, **_OPTIONAL}.items():
+    for name, (res, args) in {**_SIGNATURES, **_HYBRID, **_OPTIONAL}.items():
         try:
             fn = getattr(handle, name)
         except AttributeError:
-            if name in _OPTIONAL:
+            if name in _OPTIONAL or partial:
                 continue
             raise NativeLibraryError(f"{path} is stale: symbol {name} missing; rebuild with "
                                      "`python -m jax_llama_b200.ops.build --force`")

@@ -1,0 +1,187 @@
+"""Python front-ends of the kernels of the hybrid decoder family (csrc/seq_norm.cu, seq_linear.cu, attn_generic.cu,
+gla_scan.cu): fp32 residual stream, operands in bfloat16 or true float32, softmax attention with arbitrary head sizes
+and linear-recurrence mixers.
+
+CUDA tensors only: these ops are the product path and have no PyTorch stand-in (the numerical oracles live with the
+tests).  Every call runs on the current stream and is legal under CUDA-graph capture when the caller passes `out`
+buffers (otherwise outputs come from the caching allocator, which a torch graph capture also handles).
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .kernels import _p, _stream, ensure_gemm_workspace, num_sms
+
+ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_SILU, ACT_SCALE_SOFTCAP = 0, 1, 2, 3, 4
+ACTIVATIONS = {"none": ACT_NONE, "relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return 0
+    if dtype == torch.float32:
+        return 1
+    raise ValueError(f"the hybrid kernels run in bfloat16 or float32, not {dtype}")
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name}: the hybrid kernels take CUDA tensors only")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def tensor_cores_enabled() -> bool:
+    """JLLAMA_HYBRID_TC=0 keeps every linear layer on the exact SIMT kernels (A/B and debugging)."""
+    return os.environ.get("JLLAMA_HYBRID_TC", "1") != "0"
+
+
+def embed_f32(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    ids32 = ids.to(torch.int32).contiguous().view(-1)
+    V, W = table.shape
+    if out is None:
+        out = torch.empty((ids32.numel(), W), dtype=torch.float32, device=table.device)
+    _lib.check(_lib.lib().jl_embed_f32(ids32.data_ptr(), table.data_ptr(), out.data_ptr(), ids32.numel(), W, V,
+                                       dtype_code(table.dtype), _stream()), "jl_embed_f32")
+    return out
+
+
+def norm_f32(x: torch.Tensor, w: torch.Tensor, eps: float, offset: float, out: Optional[torch.Tensor] = None
+             ) -> torch.Tensor:
+    """x fp32 [M, W] → x / rms(x) * (offset + w) in w's dtype."""
+    _need(x, torch.float32, "x")
+    M, W = x.shape
+    if out is None:
+        out = torch.empty((M, W), dtype=w.dtype, device=x.device)
+    _lib.check(_lib.lib().jl_norm_f32(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, W, float(eps), float(offset),
+                                      dtype_code(w.dtype), _stream()), "jl_norm_f32")
+    return out
+
+
+def postnorm_add(y: torch.Tensor, w_post: torch.Tensor, x: torch.Tensor, eps: float, offset: float,
+                 w_next: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """x += norm(y) · (offset + w_post), in place; with `w_next` also returns norm(x) · (offset + w_next)."""
+    _need(y, torch.float32, "y")
+    _need(x, torch.float32, "x")
+    M, W = x.shape
+    if w_next is not None and h_out is None:
+        h_out = torch.empty((M, W), dtype=w_next.dtype, device=x.device)
+    _lib.check(_lib.lib().jl_postnorm_add(y.data_ptr(), y.stride(0), w_post.data_ptr(), x.data_ptr(), _p(w_next),
+                                          _p(h_out) if w_next is not None else 0, M, W, float(eps), float(offset),
+                                          dtype_code(w_post.dtype), _stream()), "jl_postnorm_add")
+    return h_out if w_next is not None else None
+
+
+def headnorm_gate(o: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, H: int, V: int, eps: float,
+                  gate_act: int = ACT_SILU, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """o fp32 [M, H·V]; gate: fp32 view [M, H·V] (any row pitch) → norm over V per head · w · act(gate), w's dtype."""
+    _need(o, torch.float32, "o")
+    _need(gate, torch.float32, "gate")
+    M = o.shape[0]
+    if out is None:
+        out = torch.empty((M, H * V), dtype=w.dtype, device=o.device)
+    _lib.check(_lib.lib().jl_headnorm_gate(o.data_ptr(), w.data_ptr(), gate.data_ptr(), gate.stride(0), out.data_ptr(),
+                                           M, H, V, float(eps), gate_act, dtype_code(w.dtype), _stream()),
+               "jl_headnorm_gate")
+    return out
+
+
+def act_cast(y: torch.Tensor, out_dtype: torch.dtype, act: int = ACT_NONE, p0: float = 0.0, p1: float = 0.0,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(y) for an fp32 [M, N] view into `out_dtype` (in place when out is y itself)."""
+    _need(y, torch.float32, "y")
+    M, N = y.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=y.device)
+    _lib.check(_lib.lib().jl_act_cast(y.data_ptr(), y.stride(0), out.data_ptr(), out.stride(0), M, N, act, float(p0),
+                                      float(p1), dtype_code(out_dtype), _stream()), "jl_act_cast")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, *, act: int = ACT_NONE, p0: float = 0.0, p1: float = 0.0,
+           out_f32: bool = True, out: Optional[torch.Tensor] = None, tensor_cores: Optional[bool] = None) -> torch.Tensor:
+    """act(x Wᵀ): x [M, K] and W [N, K] of one dtype (bf16 or fp32) → fp32 (or the operand dtype) [M, N].
+
+    bfloat16 with more than 8 rows and 16-byte pitches runs the tcgen05 GEMM (fp32 accumulate, fp32 out; the
+    activation is then a separate pass); 8 rows or fewer the weight-streaming kernel; everything else — true
+    float32 in particular — the exact tiled SIMT kernel."""
+    if not x.is_cuda:
+        raise ValueError("linear: CUDA tensors only")
+    _need(w, x.dtype, "w")
+    N, K = w.shape
+    M = x.numel() // K
+    x = x.view(M, K) if x.is_contiguous() else x
+    odt = torch.float32 if out_f32 else x.dtype
+    if out is None:
+        out = torch.empty((M, N), dtype=odt, device=x.device)
+    L = _lib.lib()
+    use_tc = tensor_cores_enabled() if tensor_cores is None else tensor_cores
+    if (use_tc and x.dtype == torch.bfloat16 and M > 8 and K % 8 == 0 and N % 8 == 0 and x.is_contiguous()
+            and w.is_contiguous() and out.is_contiguous() and out.shape[1] == N):
+        y = out if out.dtype == torch.float32 else torch.empty((M, N), dtype=torch.float32, device=x.device)
+        if M <= 128:
+            ensure_gemm_workspace(x.device)
+        _lib.check(L.jl_gemm(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), M, N, K, 0, 1, num_sms(x.device), _stream()),
+                   "jl_gemm")
+        if act != ACT_NONE or y is not out:
+            act_cast(y, out.dtype, act, p0, p1, out=out)
+        return out
+    _lib.check(L.jl_linear_any(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), M, N, K, act,
+                               float(p0), float(p1), dtype_code(x.dtype), int(out.dtype == torch.float32), _stream()),
+               "jl_linear_any")
+    return out
+
+
+def attn_prep(y: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor,
+              k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor,
+              rot: int, unit_norm: bool, eps: float, cache_len: torch.Tensor, pad_left: Optional[torch.Tensor],
+              B: int, S: int, H: int, G: int, D: int, Dv: int) -> None:
+    """Rotate / normalise q (and k), append k, v to the caches [B, G, T, D] / [B, G, T, Dv].  k_off < 0: queries only."""
+    _need(y, torch.float32, "y")
+    T_cap = k_cache.shape[2] if k_cache is not None else 0
+    _lib.check(_lib.lib().jl_attn_prep(
+        y.data_ptr(), y.stride(0), q_off, k_off, v_off, q_out.data_ptr(), _p(k_cache), _p(v_cache), cos.data_ptr(),
+        sin.data_ptr(), cos.shape[0], rot, int(unit_norm), float(eps), _p(cache_len), _p(pad_left), B, S, H, G, D, Dv,
+        T_cap, dtype_code(q_out.dtype), _stream()), "jl_attn_prep")
+
+
+def attn_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gate: Optional[torch.Tensor],
+                 cache_len: torch.Tensor, pad_left: Optional[torch.Tensor], B: int, S: int, H: int, scale: float,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of S new tokens per row against the (already appended) caches; gate: fp32 view [M, H]."""
+    G, T_cap, D = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    Dv = v_cache.shape[3]
+    if out is None:
+        out = torch.empty((B * S, H * Dv), dtype=q.dtype, device=q.device)
+    _lib.check(_lib.lib().jl_attn_generic(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(gate),
+        gate.stride(0) if gate is not None else 0, _p(cache_len), _p(pad_left), B, S, H, G, D, Dv, T_cap, float(scale),
+        dtype_code(q.dtype), _stream()), "jl_attn_generic")
+    return out
+
+
+def head_gate(out: torch.Tensor, gate: torch.Tensor, H: int, Dv: int) -> torch.Tensor:
+    M = out.shape[0]
+    _lib.check(_lib.lib().jl_head_gate(out.data_ptr(), gate.data_ptr(), gate.stride(0), M, H, Dv, dtype_code(out.dtype),
+                                       _stream()), "jl_head_gate")
+    return out
+
+
+def gla_scan(y: torch.Tensor, q_off: int, k_off: int, v_off: int, a_off: int, a2: torch.Tensor, a2_bias: torch.Tensor,
+             state: torch.Tensor, cache_len: Optional[torch.Tensor], pad_left: Optional[torch.Tensor], B: int, S: int,
+             H: int, D: int, Dv: int, q_scale: float, tau: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Advance the fp32 state [B, H, D, Dv] over S tokens per row; returns the raw read-outs o fp32 [B·S, H·Dv]."""
+    _need(y, torch.float32, "y")
+    _need(state, torch.float32, "state")
+    R = a2.shape[1]
+    if out is None:
+        out = torch.empty((B * S, H * Dv), dtype=torch.float32, device=y.device)
+    _lib.check(_lib.lib().jl_gla_scan(
+        y.data_ptr(), y.stride(0), q_off, k_off, v_off, a_off, a2.data_ptr(), a2_bias.data_ptr(), state.data_ptr(),
+        out.data_ptr(), _p(cache_len), _p(pad_left), B, S, H, D, Dv, R, float(q_scale), float(tau),
+        dtype_code(a2.dtype), _stream()), "jl_gla_scan")
+    return out
