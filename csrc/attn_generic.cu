@@ -75,7 +75,7 @@ struct AttnParams {
   const float* gate; int ldg;       // fp32 pre-activation of the per-head output gate (column h of row m), or nullptr
 };
 
-constexpr int AT_MAXV = 8;          // value columns per lane: Dv <= 256
+constexpr int AT_MAXV = 16;         // value columns per lane: Dv <= 512
 
 // scores of one block of 32 keys (lane = key), then the block's contribution to the output (lane = value column)
 template <typename T>

@@ -121,9 +121,13 @@ extern "C" JL_API int jl_gla_scan(const float* y, int ldy, int q_off, int k_off,
   const int cols = GS_THREADS / P;
   GlaParams p{y, ldy, q_off, k_off, v_off, a_off, B, S, H, D, Dv, R, P, q_scale, 1.0f / tau, cache_len, pad_left, state, o};
   const size_t smem = (size_t)(3 * GS_TC * P * (GS_DP + 1) + GS_TC * cols + GS_TC * R) * sizeof(float);
-  JL_CHECK_ARG(smem <= 48 * 1024, "jl_gla_scan: rank %d does not fit the staging buffer", R);
+  JL_CHECK_ARG(smem <= 200 * 1024, "jl_gla_scan: key size %d with rank %d does not fit the staging buffer", D, R);
   dim3 grid((Dv + cols - 1) / cols, H, B), block(GS_THREADS);
   count_launch();
+  if (smem > 48 * 1024) {
+    if (dtype == DT_BF16) JL_CUDA(cudaFuncSetAttribute(gla_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    else JL_CUDA(cudaFuncSetAttribute(gla_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
   JL_DISPATCH_DTYPE(dtype, gla_scan_kernel<T><<<grid, block, smem, (cudaStream_t)stream>>>(p, (const T*)a2, (const T*)a2_bias));
   JL_CUDA(cudaGetLastError());
   return JL_OK;

@@ -135,6 +135,7 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], retu
             x = x + norm_zero_centred(dense_ff(h, sub(tensors, p + "mlp.")), tensors[p + "norm2b"], eps)
         streams.append(x.clone())
     logits = norm_zero_centred(x, tensors["final.norm"], eps) @ tensors["head"].to(F64).T * cfg["logit_scale"]
-    cap = cfg["logit_softcap"]
-    logits = cap * torch.tanh(logits / cap)
+    cap = cfg.get("logit_softcap")
+    if cap:                                            # a model without a cap leaves the key out (or null / 0)
+        logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(streams)) if return_layers else logits
