@@ -27,9 +27,13 @@ struct PrepParams {
   const int* cache_len; const int* pad_left;
 };
 
+constexpr int AP_WARPS = 4;      // heads per CTA of the preparation kernel (one warp each)
+
 template <typename T>
-__global__ void attn_prep_kernel(PrepParams p, T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc) {
-  const int m = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+__global__ void __launch_bounds__(AP_WARPS * 32) attn_prep_kernel(PrepParams p, T* __restrict__ q_out, T* __restrict__ kc,
+                                                                  T* __restrict__ vc, int n_heads, int pair_loads) {
+  const int m = blockIdx.x, head = blockIdx.y * AP_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (head >= n_heads) return;
   const int b = m / p.S, s = m % p.S;
   const int slot = (p.cache_len ? *p.cache_len : 0) + s;
   int pos = slot - (p.pad_left ? p.pad_left[b] : 0);
@@ -47,23 +51,25 @@ __global__ void attn_prep_kernel(PrepParams p, T* __restrict__ q_out, T* __restr
                 : kc + (((size_t)b * p.G + (head - p.H)) * p.T + slot) * p.D;
   const float* ct = p.cos_t + (size_t)pos * (p.rot / 2);
   const float* st = p.sin_t + (size_t)pos * (p.rot / 2);
-  // pass 1: sum of squares of the rotated vector (a rotation keeps each pair's norm, but the exact statement
-  // normalises what it rotated, so the same numbers are squared here)
-  float ss = 0.0f;
-  for (int i = lane; i < p.D / 2 + (p.D & 1); i += 32) {
-    const int c0 = 2 * i, c1 = 2 * i + 1;
-    float u = src[c0], v = c1 < p.D ? src[c1] : 0.0f;
-    if (c1 < p.rot) { const float c = ct[i], sn = st[i]; const float ru = u * c - v * sn, rv = v * c + u * sn; u = ru; v = rv; }
-    ss += u * u + v * v;
-  }
+  const int npairs = p.D / 2 + (p.D & 1);
+  // pass 1 rotates and sums the squares, pass 2 rotates again (L1 hits) and writes the scaled values
   float r = 1.0f;
-  if (p.unit_norm) r = 1.0f / sqrtf(warp_sum(ss) / (float)p.D + p.eps);
-  for (int i = lane; i < p.D / 2 + (p.D & 1); i += 32) {
-    const int c0 = 2 * i, c1 = 2 * i + 1;
-    float u = src[c0], v = c1 < p.D ? src[c1] : 0.0f;
-    if (c1 < p.rot) { const float c = ct[i], sn = st[i]; const float ru = u * c - v * sn, rv = v * c + u * sn; u = ru; v = rv; }
-    dst[c0] = from_f<T>(u * r);
-    if (c1 < p.D) dst[c1] = from_f<T>(v * r);
+  for (int pass = p.unit_norm ? 0 : 1; pass < 2; ++pass) {
+    float ss = 0.0f;
+    for (int i = lane; i < npairs; i += 32) {
+      const int c0 = 2 * i, c1 = 2 * i + 1;
+      float u, v;
+      if (pair_loads) { const float2 t = *reinterpret_cast<const float2*>(src + c0); u = t.x; v = t.y; }
+      else { u = src[c0]; v = c1 < p.D ? src[c1] : 0.0f; }
+      if (c1 < p.rot) { const float c = ct[i], sn = st[i]; const float ru = u * c - v * sn, rv = v * c + u * sn; u = ru; v = rv; }
+      if (pass == 0) {
+        ss += u * u + v * v;
+      } else {
+        dst[c0] = from_f<T>(u * r);
+        if (c1 < p.D) dst[c1] = from_f<T>(v * r);
+      }
+    }
+    if (pass == 0) r = 1.0f / sqrtf(warp_sum(ss) / (float)p.D + p.eps);
   }
 }
 
@@ -205,9 +211,12 @@ extern "C" JL_API int jl_attn_prep(const float* y, int ldy, int q_off, int k_off
   JL_CHECK_ARG(rot >= 0 && rot <= D && rot % 2 == 0, "jl_attn_prep: rot=%d must be even and <= D=%d", rot, D);
   JL_CHECK_ARG(k_off >= 0 || (k_cache == nullptr && v_cache == nullptr), "jl_attn_prep: queries-only call takes no caches");
   PrepParams p{y, ldy, q_off, k_off, v_off, B, S, H, G, D, Dv, T_cap, rot, cos_t, sin_t, max_pos, unit_norm, eps, cache_len, pad_left};
-  dim3 grid(B * S, k_off >= 0 ? H + 2 * G : H);
+  const int n_heads = k_off >= 0 ? H + 2 * G : H;
+  const int pair_loads = D % 2 == 0 && ldy % 2 == 0 && q_off % 2 == 0 && (k_off < 0 || k_off % 2 == 0) && (uintptr_t)y % 8 == 0;
+  dim3 grid(B * S, (n_heads + AP_WARPS - 1) / AP_WARPS);
   count_launch();
-  JL_DISPATCH_DTYPE(dtype, attn_prep_kernel<T><<<grid, 32, 0, (cudaStream_t)stream>>>(p, (T*)q_out, (T*)k_cache, (T*)v_cache));
+  JL_DISPATCH_DTYPE(dtype, attn_prep_kernel<T><<<grid, AP_WARPS * 32, 0, (cudaStream_t)stream>>>(p, (T*)q_out, (T*)k_cache,
+                                                                                                (T*)v_cache, n_heads, pair_loads));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

@@ -1,7 +1,8 @@
 // Linear layers for any shape and for bfloat16 or true float32 operands: y = act(x W^T) with W [N, K] (out, in).
 //
-//  * linear_rows_kernel  (M <= 8: decode)  — weight-streaming: a warp owns ROWS output features, reads their weight rows once
-//    (16-byte loads where the pitch allows) and keeps ROWS x M fp32 accumulators; activations come from L1.
+//  * linear_rows_kernel  (M <= 8: decode)  — weight-streaming: a CTA owns ROWS output features, its 8 warps split K, each
+//    lane reads 16 bytes of every row per step (all loads issued before the first use) and keeps ROWS x M fp32
+//    accumulators; activations come from L1; the warps' sums meet in shared memory in a fixed order.
 //  * linear_tiled_kernel (any M)           — 64 x 64 x 16 shared-memory tiles, 4 x 4 outputs per thread, fp32 FMA.  This is
 //    the exact float32 path and the fall-back for pitches the tensor-core GEMM does not take.
 //
@@ -30,13 +31,15 @@ template <> __device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_b
   v[4] = bf16_lo(t.z); v[5] = bf16_hi(t.z); v[6] = bf16_lo(t.w); v[7] = bf16_hi(t.w);
 }
 
+constexpr int LR_WARPS = 8;     // warps of a CTA: they split K for the same LR_ROWS output features
+
 template <typename T, typename OutT, int M>
-__global__ void __launch_bounds__(128) linear_rows_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w,
-                                                          OutT* __restrict__ out, int ldo, int N, int K, int act, float p0,
-                                                          float p1, int vec_ok) {
-  const int lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * LR_ROWS;
-  if (n0 >= N) return;
+__global__ void __launch_bounds__(LR_WARPS * 32) linear_rows_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w,
+                                                                    OutT* __restrict__ out, int ldo, int N, int K, int act,
+                                                                    float p0, float p1, int vec_ok) {
+  __shared__ float red[LR_WARPS][LR_ROWS][M];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n0 = blockIdx.x * LR_ROWS;
   float acc[LR_ROWS][M];
 #pragma unroll
   for (int r = 0; r < LR_ROWS; ++r)
@@ -46,32 +49,31 @@ __global__ void __launch_bounds__(128) linear_rows_kernel(const T* __restrict__ 
   int k_done = 0;
   if (vec_ok) {
     const int kv = K / VN * VN;
-    for (int k = lane * VN; k < kv; k += 32 * VN) {
-      float xv[M][VN];
+    for (int k = (warp * 32 + lane) * VN; k < kv; k += LR_WARPS * 32 * VN) {
+      float wv[LR_ROWS][VN];
 #pragma unroll
-      for (int m = 0; m < M; ++m) load_vec<T>(x + (size_t)m * ldx + k, xv[m]);
+      for (int r = 0; r < LR_ROWS; ++r) {          // all weight loads of this step are in flight before any is used
+        const int n = min(n0 + r, N - 1);
+        load_vec<T>(w + (size_t)n * K + k, wv[r]);
+      }
 #pragma unroll
-      for (int r = 0; r < LR_ROWS; ++r) {
-        if (n0 + r < N) {
-          float wv[VN];
-          load_vec<T>(w + (size_t)(n0 + r) * K + k, wv);
+      for (int m = 0; m < M; ++m) {
+        float xv[VN];
+        load_vec<T>(x + (size_t)m * ldx + k, xv);
 #pragma unroll
-          for (int m = 0; m < M; ++m)
+        for (int r = 0; r < LR_ROWS; ++r)
 #pragma unroll
-            for (int j = 0; j < VN; ++j) acc[r][m] = fmaf(wv[j], xv[m][j], acc[r][m]);
-        }
+          for (int j = 0; j < VN; ++j) acc[r][m] = fmaf(wv[r][j], xv[j], acc[r][m]);
       }
     }
     k_done = kv;
   }
-  for (int k = k_done + lane; k < K; k += 32) {
+  for (int k = k_done + warp * 32 + lane; k < K; k += LR_WARPS * 32) {
 #pragma unroll
     for (int r = 0; r < LR_ROWS; ++r) {
-      if (n0 + r < N) {
-        const float wv = to_f(w[(size_t)(n0 + r) * K + k]);
+      const float wv = to_f(w[(size_t)min(n0 + r, N - 1) * K + k]);
 #pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = fmaf(wv, to_f(x[(size_t)m * ldx + k]), acc[r][m]);
-      }
+      for (int m = 0; m < M; ++m) acc[r][m] = fmaf(wv, to_f(x[(size_t)m * ldx + k]), acc[r][m]);
     }
   }
 #pragma unroll
@@ -79,8 +81,16 @@ __global__ void __launch_bounds__(128) linear_rows_kernel(const T* __restrict__ 
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       const float s = warp_sum(acc[r][m]);
-      if (lane == 0 && n0 + r < N) out[(size_t)m * ldo + n0 + r] = from_f<OutT>(apply_act(s, act, p0, p1));
+      if (lane == 0) red[warp][r][m] = s;
     }
+  __syncthreads();
+  if (threadIdx.x < LR_ROWS * M) {
+    const int r = threadIdx.x / M, m = threadIdx.x % M;
+    float s = 0.0f;
+#pragma unroll
+    for (int wq = 0; wq < LR_WARPS; ++wq) s += red[wq][r][m];
+    if (n0 + r < N) out[(size_t)m * ldo + n0 + r] = from_f<OutT>(apply_act(s, act, p0, p1));
+  }
 }
 
 constexpr int LT_BM = 64, LT_BN = 64, LT_BK = 16;
@@ -133,10 +143,10 @@ static int launch_linear(const void* x, int ldx, const void* w, void* out, int l
   if (M <= LR_MAXM) {
     constexpr int VN = Vec<T>::N;
     const int vec_ok = (K % VN == 0) && (ldx % VN == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0);
-    const int warps = 4, blocks = ((N + LR_ROWS - 1) / LR_ROWS + warps - 1) / warps;
+    const int blocks = (N + LR_ROWS - 1) / LR_ROWS;
 #define JL_LR(MM)                                                                                                       \
   case MM:                                                                                                              \
-    linear_rows_kernel<T, OutT, MM><<<blocks, warps * 32, 0, st>>>((const T*)x, ldx, (const T*)w, (OutT*)out, ldo, N, K, act, \
+    linear_rows_kernel<T, OutT, MM><<<blocks, LR_WARPS * 32, 0, st>>>((const T*)x, ldx, (const T*)w, (OutT*)out, ldo, N, K, act, \
                                                                    p0, p1, vec_ok);                                     \
     break;
     switch (M) { JL_LR(1) JL_LR(2) JL_LR(3) JL_LR(4) JL_LR(5) JL_LR(6) JL_LR(7) JL_LR(8) }

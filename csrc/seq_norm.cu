@@ -52,6 +52,71 @@ __global__ void postnorm_add_kernel(const float* __restrict__ y, int ldy, const 
     h[(size_t)blockIdx.x * W + i] = from_f<T>(xr[i] * r2 * (offset + to_f(w_next[i])));
 }
 
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  v[0] = bf16_lo(t.x); v[1] = bf16_hi(t.x); v[2] = bf16_lo(t.y); v[3] = bf16_hi(t.y);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+}
+
+// The same step with the row held in registers: 16-byte loads, x and y read once, x and h written once.
+// W % 4 == 0, ldy % 4 == 0, W <= 256 * 4 * VPT.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256) postnorm_add_vec_kernel(const float* __restrict__ y, int ldy, const T* __restrict__ w_post,
+                                                               float* __restrict__ x, const T* __restrict__ w_next,
+                                                               T* __restrict__ h, int W, float eps, float offset) {
+  __shared__ float red[33];
+  const float* yr = y + (size_t)blockIdx.x * ldy;
+  float* xr = x + (size_t)blockIdx.x * W;
+  const int nv = W / 4;
+  float yv[VPT][4], xv[VPT][4];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    if (idx < nv) {
+      load4(yr + 4 * idx, yv[i]);
+      load4(xr + 4 * idx, xv[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ss += yv[i][j] * yv[i][j];
+    }
+  }
+  const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
+  float s2 = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    if (idx < nv) {
+      float wv[4];
+      load4(w_post + 4 * idx, wv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { xv[i][j] += yv[i][j] * r * (offset + wv[j]); s2 += xv[i][j] * xv[i][j]; }
+      store4(xr + 4 * idx, xv[i]);
+    }
+  }
+  if (w_next == nullptr) return;
+  const float r2 = 1.0f / sqrtf(block_sum(s2, red) / (float)W + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    if (idx < nv) {
+      float wv[4], hv[4];
+      load4(w_next + 4 * idx, wv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) hv[j] = xv[i][j] * r2 * (offset + wv[j]);
+      store4(h + (size_t)blockIdx.x * W + 4 * idx, hv);
+    }
+  }
+}
+
 // One warp per (token, head): out = o / sqrt(mean_v(o^2) + eps) * w[v] * act(gate)
 template <typename T>
 __global__ void headnorm_gate_kernel(const float* __restrict__ o, const T* __restrict__ w, const float* __restrict__ gate,
@@ -79,9 +144,44 @@ __global__ void act_cast_kernel(const float* __restrict__ in, int ldi, OutT* __r
   }
 }
 
+// data[m, n] = act(data[m, n]) in place, 16 bytes per thread and step where the pitch allows
+template <typename T>
+__global__ void act_inplace_kernel(T* __restrict__ data, int ld, int M, int N, int act, float p0, float p1, int vec) {
+  constexpr int VN = 16 / sizeof(T);
+  if (vec) {
+    const size_t per_row = N / VN, total = (size_t)M * per_row;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+      T* ptr = data + (idx / per_row) * ld + (idx % per_row) * VN;
+      uint4 raw = *reinterpret_cast<uint4*>(ptr);
+      T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) e[j] = from_f<T>(apply_act(to_f(e[j]), act, p0, p1));
+      *reinterpret_cast<uint4*>(ptr) = raw;
+    }
+    return;
+  }
+  const size_t total = (size_t)M * N;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    T* ptr = data + (idx / N) * ld + idx % N;
+    *ptr = from_f<T>(apply_act(to_f(*ptr), act, p0, p1));
+  }
+}
+
 }  // namespace jl
 
 using namespace jl;
+
+extern "C" JL_API int jl_act_inplace(void* data, int ld, int M, int N, int act, float p0, float p1, int dtype, void* stream) {
+  JL_CHECK_ARG(M >= 1 && N >= 1 && ld >= N, "jl_act_inplace: bad shape M=%d N=%d ld=%d", M, N, ld);
+  const int vn = dtype == DT_BF16 ? 8 : 4;
+  const int vec = N % vn == 0 && ld % vn == 0 && (uintptr_t)data % 16 == 0;
+  const size_t work = (size_t)M * N / (vec ? vn : 1);
+  const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
+  count_launch();
+  JL_DISPATCH_DTYPE(dtype, act_inplace_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)data, ld, M, N, act, p0, p1, vec));
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
 
 extern "C" JL_API int jl_embed_f32(const int* ids, const void* table, float* out, int M, int W, int V, int dtype, void* stream) {
   JL_CHECK_ARG(M >= 1 && W >= 1 && V >= 1, "jl_embed_f32: bad shape M=%d W=%d V=%d", M, W, V);
@@ -105,6 +205,18 @@ extern "C" JL_API int jl_postnorm_add(const float* y, int ldy, const void* w_pos
   JL_CHECK_ARG(M >= 1 && W >= 1 && ldy >= W, "jl_postnorm_add: bad shape M=%d W=%d ldy=%d", M, W, ldy);
   JL_CHECK_ARG((w_next == nullptr) == (h == nullptr), "jl_postnorm_add: w_next and h come together");
   count_launch();
+  const bool vec = W % 4 == 0 && ldy % 4 == 0 && W <= 256 * 4 * 16 && (uintptr_t)y % 16 == 0 && (uintptr_t)x % 16 == 0 &&
+                   (uintptr_t)w_post % 16 == 0 && (uintptr_t)w_next % 16 == 0 && (uintptr_t)h % 16 == 0;
+  if (vec) {
+    const int vpt = (W / 4 + 255) / 256;
+#define JL_PN(V)                                                                                                         \
+  JL_DISPATCH_DTYPE(dtype, postnorm_add_vec_kernel<T, V><<<M, 256, 0, (cudaStream_t)stream>>>(y, ldy, (const T*)w_post, x, \
+                                                                                               (const T*)w_next, (T*)h, W, eps, offset))
+    if (vpt <= 1) JL_PN(1); else if (vpt <= 2) JL_PN(2); else if (vpt <= 4) JL_PN(4); else if (vpt <= 8) JL_PN(8); else JL_PN(16);
+#undef JL_PN
+    JL_CUDA(cudaGetLastError());
+    return JL_OK;
+  }
   JL_DISPATCH_DTYPE(dtype, postnorm_add_kernel<T><<<M, 256, 0, (cudaStream_t)stream>>>(y, ldy, (const T*)w_post, x,
                                                                                         (const T*)w_next, (T*)h, W, eps, offset));
   JL_CUDA(cudaGetLastError());

@@ -277,6 +277,8 @@ int jl_headnorm_gate(const float* o, const void* w, const float* gate, int ldg, 
  * 3 silu, 4 scale by p0 then soft cap p1 * tanh(. / p1) (p1 <= 0: no cap). */
 int jl_act_cast(const float* in, int ldi, void* out, int ldo, int M, int N, int act, float p0, float p1, int out_dtype,
                 void* stream);
+/* data = act(data) in place for an [M, N] block (pitch ld) of dtype. */
+int jl_act_inplace(void* data, int ld, int M, int N, int act, float p0, float p1, int dtype, void* stream);
 /* out[:, 0:N] (pitch ldo; fp32 if out_f32 else dtype) = act(x W^T): x [M, K] (pitch ldx), W [N, K]; any M, N, K. */
 int jl_linear_any(const void* x, int ldx, const void* w, void* out, int ldo, int M, int N, int K, int act, float p0, float p1,
                   int dtype, int out_f32, void* stream);
@@ -292,10 +294,13 @@ int jl_attn_generic(const void* q, const void* k_cache, const void* v_cache, voi
                     int dtype, void* stream);
 /* out[m, h, :] *= sigmoid(gate[m, h]) in place. */
 int jl_head_gate(void* out, const float* gate, int ldg, int M, int H, int Dv, int dtype, void* stream);
-/* Gated linear attention scan: state [B][H][D][Dv] fp32 (in/out), o fp32 [B*S, H, Dv]; a2 [H*D, R], a2_bias [H*D] of dtype. */
+/* Gated linear attention scan: state [B][H][D][Dv] fp32 (in/out), o fp32 [B*S, H, Dv]; a2 [H*D, R], a2_bias [H*D] of dtype.
+ * ws == NULL: one fused launch (decoding).  ws = jl_gla_scan_ws_floats(...) floats: token-parallel preparation into ws, then
+ * a scan that streams it through a two-stage cp.async pipeline (prompts). */
+size_t jl_gla_scan_ws_floats(int B, int S, int H, int D, int Dv);
 int jl_gla_scan(const float* y, int ldy, int q_off, int k_off, int v_off, int a_off, const void* a2, const void* a2_bias,
                 float* state, float* o, const int* cache_len, const int* pad_left, int B, int S, int H, int D, int Dv, int R,
-                float q_scale, float tau, int dtype, void* stream);
+                float q_scale, float tau, float* ws, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -17,6 +17,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config import AttentionMixerSpec, GlaMixerSpec
+from ..ops import _lib
 from ..ops import kernels as K
 from ..ops import seq_kernels as SK
 
@@ -59,6 +60,7 @@ class AttentionMixer:
         self.g_off = offs[-1] if spec.head_gate else -1
         self.wo = w["o"].contiguous()
         self.dtype = self.wo.dtype
+        self._decode_plans: Dict[Tuple[int, int], Tuple[int, Optional[torch.Tensor]]] = {}
 
     def weights(self) -> List[torch.Tensor]:
         return [self.w_in, self.wo]
@@ -85,23 +87,39 @@ class AttentionMixer:
                      None if self.shares_kv else vc, rope[0], rope[1], rot, s.qk_unit_norm, self.eps, cache.len_dev,
                      cache.pad_left, B, S, s.heads, s.kv_heads, s.dim, s.vdim)
         gate = y[:, self.g_off:self.g_off + s.heads] if s.head_gate else None
-        if self._tensor_core_shape(S):
-            # 128-wide heads in bfloat16: the tcgen05 flash kernel (prompts) / the split-KV decode kernel
-            out = self._attend_tensor_cores(q, kc, vc, cache, B, S)
+        if self._library_shape():
+            # 64- / 128-wide heads in bfloat16 are the shapes the LLaMA kernels are built for: the tcgen05 flash kernel
+            # for prompts, the split-KV kernel for one new token; both take the score scale as an argument
+            out = self._attend_shared_kernels(q, kc, vc, cache, B, S)
             if gate is not None:
-                SK.head_gate(out.view(B * S, -1), gate, s.heads, s.vdim)
-            return out.view(B * S, s.heads * s.vdim)
+                SK.head_gate(out, gate, s.heads, s.vdim)
+            return out
         return SK.attn_generic(q, kc, vc, gate, cache.len_dev, cache.pad_left, B, S, s.heads, s.scale)
 
-    def _tensor_core_shape(self, S: int) -> bool:
+    def _library_shape(self) -> bool:
         s = self.spec
-        return (SK.tensor_cores_enabled() and self.dtype == torch.bfloat16 and s.dim == 128 and s.vdim == 128
-                and S > 1 and abs(s.scale - 1.0 / math.sqrt(s.dim)) < 1e-12)
+        return (SK.tensor_cores_enabled() and self.dtype == torch.bfloat16 and s.dim == s.vdim and s.dim in (64, 128)
+                and s.heads // s.kv_heads in (1, 2, 4, 8))
 
-    def _attend_tensor_cores(self, q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, cache: "object", B: int, S: int
-                             ) -> torch.Tensor:
+    def _attend_shared_kernels(self, q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, cache: "object", B: int, S: int
+                               ) -> torch.Tensor:
         s = self.spec
-        return K.prefill_attn(q.view(B, S, s.heads, s.dim), kc, vc, cache.index, S, cache.pad_left, cache.len_dev)
+        L = _lib.lib()
+        out = torch.empty((B * S, s.heads * s.vdim), dtype=self.dtype, device=q.device)
+        T = kc.shape[2]
+        if S > 1:
+            _lib.check(L.jl_flash_prefill(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), cache.len_dev.data_ptr(),
+                                          cache.pad_left.data_ptr(), out.data_ptr(), B, S, s.heads, s.kv_heads, s.dim, T,
+                                          int(cache.index), float(s.scale), K._stream()), "jl_flash_prefill")
+            return out
+        key = (B, T)
+        if key not in self._decode_plans:
+            self._decode_plans[key] = K.decode_attn_plan(B, s.heads, s.kv_heads, s.dim, T, q.device)
+        splits, scratch = self._decode_plans[key]
+        _lib.check(L.jl_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), cache.len_dev.data_ptr(),
+                                    cache.pad_left.data_ptr(), K._p(scratch), out.data_ptr(), B, s.heads, s.kv_heads, s.dim,
+                                    T, 1, float(s.scale), splits, 0, K._stream()), "jl_decode_attn")
+        return out
 
 
 class GlaMixer:

@@ -17,6 +17,7 @@ from . import _lib
 from .kernels import _p, _stream, ensure_gemm_workspace, num_sms
 
 ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_SILU, ACT_SCALE_SOFTCAP = 0, 1, 2, 3, 4
+GLA_FUSED_MAX_TOKENS = 8      # up to this many tokens per row the gated-linear-attention scan stays one fused launch
 ACTIVATIONS = {"none": ACT_NONE, "relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU}
 
 
@@ -106,8 +107,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, act: int = ACT_NONE, p0: float =
            out_f32: bool = True, out: Optional[torch.Tensor] = None, tensor_cores: Optional[bool] = None) -> torch.Tensor:
     """act(x Wᵀ): x [M, K] and W [N, K] of one dtype (bf16 or fp32) → fp32 (or the operand dtype) [M, N].
 
-    bfloat16 with more than 8 rows and 16-byte pitches runs the tcgen05 GEMM (fp32 accumulate, fp32 out; the
-    activation is then a separate pass); 8 rows or fewer the weight-streaming kernel; everything else — true
+    bfloat16 with more than 8 rows and 16-byte pitches runs the tcgen05 GEMM (fp32 accumulate; the activation is
+    then an in-place pass over the stored result); 8 rows or fewer the weight-streaming kernel; everything else — true
     float32 in particular — the exact tiled SIMT kernel."""
     if not x.is_cuda:
         raise ValueError("linear: CUDA tensors only")
@@ -122,13 +123,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, act: int = ACT_NONE, p0: float =
     use_tc = tensor_cores_enabled() if tensor_cores is None else tensor_cores
     if (use_tc and x.dtype == torch.bfloat16 and M > 8 and K % 8 == 0 and N % 8 == 0 and x.is_contiguous()
             and w.is_contiguous() and out.is_contiguous() and out.shape[1] == N):
-        y = out if out.dtype == torch.float32 else torch.empty((M, N), dtype=torch.float32, device=x.device)
         if M <= 128:
             ensure_gemm_workspace(x.device)
-        _lib.check(L.jl_gemm(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), M, N, K, 0, 1, num_sms(x.device), _stream()),
-                   "jl_gemm")
-        if act != ACT_NONE or y is not out:
-            act_cast(y, out.dtype, act, p0, p1, out=out)
+        f32 = out.dtype == torch.float32
+        _lib.check(L.jl_gemm(x.data_ptr(), w.data_ptr(), None, out.data_ptr(), M, N, K, 0, int(f32), num_sms(x.device),
+                             _stream()), "jl_gemm")
+        if act != ACT_NONE:
+            # the activation runs on the stored result (bf16 results: on the rounded value), in place
+            _lib.check(L.jl_act_inplace(out.data_ptr(), out.stride(0), M, N, act, float(p0), float(p1),
+                                        dtype_code(out.dtype), _stream()), "jl_act_inplace")
         return out
     _lib.check(L.jl_linear_any(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), M, N, K, act,
                                float(p0), float(p1), dtype_code(x.dtype), int(out.dtype == torch.float32), _stream()),
@@ -180,8 +183,12 @@ def gla_scan(y: torch.Tensor, q_off: int, k_off: int, v_off: int, a_off: int, a2
     R = a2.shape[1]
     if out is None:
         out = torch.empty((B * S, H * Dv), dtype=torch.float32, device=y.device)
-    _lib.check(_lib.lib().jl_gla_scan(
+    L = _lib.lib()
+    ws = None
+    if S > GLA_FUSED_MAX_TOKENS:          # prompts: token-parallel preparation + pipelined scan (two launches)
+        ws = torch.empty(int(L.jl_gla_scan_ws_floats(B, S, H, D, Dv)), dtype=torch.float32, device=y.device)
+    _lib.check(L.jl_gla_scan(
         y.data_ptr(), y.stride(0), q_off, k_off, v_off, a_off, a2.data_ptr(), a2_bias.data_ptr(), state.data_ptr(),
-        out.data_ptr(), _p(cache_len), _p(pad_left), B, S, H, D, Dv, R, float(q_scale), float(tau),
+        out.data_ptr(), _p(cache_len), _p(pad_left), B, S, H, D, Dv, R, float(q_scale), float(tau), _p(ws),
         dtype_code(a2.dtype), _stream()), "jl_gla_scan")
     return out

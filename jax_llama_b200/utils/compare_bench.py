@@ -1,0 +1,269 @@
+"""Side-by-side throughput of a hybrid (Folirax) model and the LLaMA model of equal width, depth and head sizes, with
+random weights, plus the time of each kernel of the new design beside the like kernel of the LLaMA path.
+
+Used by ``bench.py --compare folirax``.  Everything is timed with CUDA events on the launching stream after warm-up;
+per-kernel timings flush L2 (a 256 MB write) between iterations, whole-model timings stream more weight bytes than
+L2 holds.  Fractions are of the measured peaks in MEASURED_PEAKS.json (HBM copy bandwidth, cuBLAS bf16 burst).
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+from typing import Any, Callable, Dict, List
+
+import torch
+
+SIZES: Dict[str, Dict[str, int]] = {
+    # width, heads x 128 attention (kv heads), ff, layers, vocab
+    "w2048": dict(width=2048, heads=16, kv_heads=4, ff=8192, layers=8, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, ff=14336, layers=4, vocab=32000),
+}
+
+
+def folirax_config(s: Dict[str, int]) -> Any:
+    from ..config import FoliraxConfig
+
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "rot": {"dims": 64, "base": 10000.0}}
+    gla = {"heads": s["heads"], "dim": 64, "vdim": 128, "tau": 16.0}
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    block = [{"type": "gla", "mixer": gla, "mlp": None}, {"type": "attention", "mixer": att, "mlp": mlp},
+             {"type": "attention", "mixer": dict(att, kv_from=None), "mlp": mlp}, {"type": "gla", "mixer": gla, "mlp": mlp}]
+    layers: List[Dict[str, Any]] = []
+    for i in range(s["layers"]):
+        l = json.loads(json.dumps(block[i % 4]))
+        if i % 4 == 2:
+            l["mixer"]["kv_from"] = i - 1
+        layers.append(l)
+    return FoliraxConfig.from_dict({"architecture": "Folirax", "vocab": s["vocab"], "width": s["width"],
+                                    "norm": {"eps": 1e-5}, "logit_scale": 0.5, "logit_softcap": 30.0, "layers": layers})
+
+
+def llama_config(s: Dict[str, int]) -> Any:
+    from ..config import LLaMAConfig
+
+    return LLaMAConfig(vocab_size=s["vocab"], hidden_size=s["width"], intermediate_size=s["ff"],
+                       num_hidden_layers=s["layers"], num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"],
+                       max_sequence_length=4096, rms_norm_eps=1e-5)
+
+
+class Timer:
+    def __init__(self, device: torch.device):
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def kernel(self, fn: Callable[[], Any], reps: int = 10) -> float:
+        """Median ms of one call of fn with a cold L2."""
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            self.flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+
+def _model_times(eng: Any, vocab: int, prompt_len: int, batches: List[int], steps: int, warmup: int) -> Dict[str, Any]:
+    dev = eng.device
+    out: Dict[str, Any] = {}
+    g = torch.Generator().manual_seed(7)
+    for B in batches:
+        ids = torch.randint(1, vocab, (B, prompt_len), generator=g).to(dev)
+        max_len = prompt_len + warmup + steps + 8
+        st = eng._decode_state(B, max_len)
+        pre = []
+        for i in range(4):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.prepare(st, ids, None, 0)
+            e1.record()
+            torch.cuda.synchronize()
+            if i:
+                pre.append(e0.elapsed_time(e1))
+        stream = eng.begin_stream(ids, None, max_length=max_len, eos_token_id=-1)
+        for _ in range(warmup):
+            stream.graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            stream.graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        out[f"batch{B}"] = {"prefill_ms": round(min(pre), 3), "prefill_tokens_per_sec": round(B * prompt_len / min(pre) * 1e3, 1),
+                            "decode_ms_per_step": round(ms, 4), "decode_tokens_per_sec": round(B / ms * 1e3, 1),
+                            "launches_per_decode_step": eng.launches_per_step(st)}
+        stream.close()
+    out["weight_bytes_per_step"] = eng.weight_bytes_per_step()
+    return out
+
+
+def _kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str, float], prompt_len: int) -> List[Dict[str, Any]]:
+    """Each kernel of the new design at this size beside the like kernel of the LLaMA path: ms, achieved rate, and the
+    fraction of the measured roofline (HBM copy peak for memory-bound kernels, cuBLAS bf16 burst for GEMM-shaped ones)."""
+    from ..models.mixers import rotary_table
+    from ..models.reference import rope_cos_sin
+    from ..ops import _lib as L
+    from ..ops import kernels as K
+    from ..ops import seq_kernels as SK
+
+    t = Timer(dev)
+    hbm, tf = peaks["hbm_gbs"], peaks["bf16_tflops"]
+    W, H, G, F = s["width"], s["heads"], s["kv_heads"], s["ff"]
+    D = Dv = 128
+    gd, gv, R = 64, 128, 16
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    rows: List[Dict[str, Any]] = []
+
+    def add(name: str, ms: float, like: str, like_ms: float, nbytes: float = 0.0, flops: float = 0.0, note: str = "",
+            like_nbytes: float = 0.0) -> None:
+        r: Dict[str, Any] = {"kernel": name, "ms": round(ms, 4), "like": like, "like_ms": round(like_ms, 4) if like_ms else None}
+        if nbytes:
+            r["gbs"] = round(nbytes / ms / 1e6, 1)
+            r["frac_hbm_of_measured"] = round(nbytes / ms / 1e6 / hbm, 3)
+            if like_ms:
+                r["like_frac"] = round((like_nbytes or nbytes) / like_ms / 1e6 / hbm, 3)
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["frac_bf16_of_measured"] = round(flops / ms / 1e9 / tf, 3)
+            if like_ms:
+                r["like_frac"] = round(flops / like_ms / 1e9 / tf, 3)
+        if note:
+            r["note"] = note
+        rows.append(r)
+
+    # ---- decode, one row: stacked input projection of a recurrent layer / fused qkv of LLaMA (weight streaming)
+    n_in = 2 * H * gd + 2 * H * gv + R
+    n_in += (-n_in) % 8
+    w = torch.randn(n_in, W, **bf) * 0.02
+    x = torch.randn(1, W, **bf)
+    add("linear_rows (stacked projection, M=1)", t.kernel(lambda: SK.linear(x, w)), "gemv_kernel",
+        t.kernel(lambda: K.linear(x, w, out_f32=True)), nbytes=w.numel() * 2)
+    wd = torch.randn(W, F, **bf) * 0.02
+    xf = torch.randn(1, F, **bf)
+    add("linear_rows (ff down, M=1)", t.kernel(lambda: SK.linear(xf, wd)), "gemv_kernel",
+        t.kernel(lambda: K.linear(xf, wd, out_f32=True)), nbytes=wd.numel() * 2)
+    x8 = torch.randn(8, W, **bf)
+    add("linear_rows (stacked projection, M=8)", t.kernel(lambda: SK.linear(x8, w)), "gemv_kernel (M=8)",
+        t.kernel(lambda: K.linear(x8, w, out_f32=True, force="gemv")), nbytes=w.numel() * 2)
+
+    # ---- prefill GEMM: the same tcgen05 kernel, fp32 result + activation pass vs bf16 result
+    xp = torch.randn(prompt_len, W, **bf)
+    wu = torch.randn(F, W, **bf) * 0.02
+    fl = 2.0 * prompt_len * F * W
+    add("tcgen05 GEMM fp32 out + relu^2 pass (ff up)", t.kernel(lambda: SK.linear(xp, wu, act=SK.ACT_RELU2, out_f32=False)),
+        "tcgen05 GEMM bf16 out (same N, K)", t.kernel(lambda: K.linear(xp, wu)), flops=fl)
+
+    # ---- norms
+    xr = torch.randn(prompt_len, W, device=dev)
+    yr = torch.randn(prompt_len, W, device=dev)
+    wn = torch.zeros(W, **bf)
+    xb, db = xr.to(torch.bfloat16), yr.to(torch.bfloat16)
+    add("postnorm_add (+ next norm), fp32 stream", t.kernel(lambda: SK.postnorm_add(yr, wn, xr, 1e-5, 1.0, w_next=wn)),
+        "rmsnorm_kernel (+ residual), bf16 stream", t.kernel(lambda: K.rmsnorm(xb, wn, 1e-5, delta=db)),
+        nbytes=prompt_len * W * (4 + 4 + 4 + 2), like_nbytes=prompt_len * W * 8,
+        note="like kernel moves 8 B per element, this one 14 B (fp32 residual)")
+
+    # ---- attention, prompt and one token at a 2k context
+    T = prompt_len + 8
+    cos, sin = rotary_table(64, 10000.0, T, dev)
+    y = torch.randn(prompt_len, (H + 2 * G) * D + 8, device=dev)
+    q = torch.empty(prompt_len, H * D, **bf)
+    kc, vc = torch.zeros(1, G, T, D, **bf), torch.zeros(1, G, T, Dv, **bf)
+    zero, pad = torch.zeros(1, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+    prep = lambda: SK.attn_prep(y, 0, H * D, (H + G) * D, q, kc, vc, cos, sin, 64, True, 1e-5, zero, pad, 1, prompt_len,  # noqa: E731
+                                H, G, D, Dv)
+    prep()
+    lc, ls = (c.to(dev) for c in rope_cos_sin(D, T, 10000.0))
+    qkv = torch.randn(prompt_len, (H + 2 * G) * D, **bf)
+    q2 = torch.empty(prompt_len, H * D, **bf)
+    add("attn_prep (rotary + unit norm + append), prompt", t.kernel(prep), "rope_kv_kernel",
+        t.kernel(lambda: K.rope_kv_write(qkv, kc, vc, lc, ls, 1, prompt_len, H, G, D, cache_len=zero, pad_left=pad, q_out=q2)),
+        nbytes=prompt_len * (H + 2 * G) * D * (4 + 2), like_nbytes=prompt_len * (H + 2 * G) * D * (2 + 2),
+        note="reads the fp32 projection (4 B) where the like kernel reads bf16")
+    causal = 4.0 * prompt_len * prompt_len / 2 * D * H
+    out = torch.empty(prompt_len, H * Dv, **bf)
+    flash = lambda: L.check(L.lib().jl_flash_prefill(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), zero.data_ptr(), pad.data_ptr(),  # noqa: E731
+                                                     out.data_ptr(), 1, prompt_len, H, G, D, T, 0, D ** -0.5, K._stream()), "flash")
+    ms_flash = t.kernel(flash)
+    gate = y[:, :H]
+    add("flash_prefill_kernel + head_gate pass", ms_flash + t.kernel(lambda: SK.head_gate(out, gate, H, Dv)),
+        "flash_prefill_kernel", ms_flash, flops=causal)
+    add("attn_rows_kernel (exact SIMT, any head size)", t.kernel(lambda: SK.attn_generic(q, kc, vc, gate, zero, pad, 1, prompt_len, H, D ** -0.5), reps=3),
+        "flash_prefill_kernel", ms_flash, flops=causal, note="fall-back for head sizes other than 64 / 128 and for float32")
+    ctx = torch.full((1,), prompt_len, dtype=torch.int32, device=dev)
+    q1 = torch.randn(1, H * D, **bf)
+    kv_bytes = 2.0 * G * prompt_len * D * 2
+    splits, scratch = K.decode_attn_plan(1, H, G, D, T, dev)
+    o1 = torch.empty(1, H * Dv, **bf)
+    dec = lambda: L.check(L.lib().jl_decode_attn(q1.data_ptr(), kc.data_ptr(), vc.data_ptr(), ctx.data_ptr(), pad.data_ptr(),  # noqa: E731
+                                                 K._p(scratch), o1.data_ptr(), 1, H, G, D, T, 1, D ** -0.5, splits, 0, K._stream()), "dec")
+    ms_dec = t.kernel(dec)
+    add("decode_attn_kernel (shared) + head_gate", ms_dec + t.kernel(lambda: SK.head_gate(o1, gate[:1], H, Dv)),
+        "decode_attn_kernel", ms_dec, nbytes=kv_bytes)
+    add("attn_decode_kernel (exact SIMT, any head size)", t.kernel(lambda: SK.attn_generic(q1, kc, vc, gate[:1], ctx, pad, 1, 1, H, D ** -0.5)),
+        "decode_attn_kernel", ms_dec, nbytes=kv_bytes, note="one CTA per (row, head): fall-back shapes only")
+
+    # ---- gated linear attention: no like kernel in the LLaMA path
+    n_y = 2 * H * gd + 2 * H * gv + R
+    yg = torch.randn(prompt_len, n_y, device=dev) * 0.3
+    a2 = torch.randn(H * gd, R, **bf) * 0.1
+    a2b = torch.full((H * gd,), 3.0, **bf)
+    state = torch.zeros(1, H, gd, gv, device=dev)
+    scan = lambda S: SK.gla_scan(yg[:S], 0, H * gd, 2 * H * gd, 2 * H * gd + 2 * H * gv, a2, a2b, state, zero, pad, 1, S, H, gd, gv,  # noqa: E731
+                                 gd ** -0.5, 16.0)
+    ms = t.kernel(lambda: scan(prompt_len), reps=5)
+    add("gla_scan_kernel, prompt", ms, "(none)", 0.0, flops=0.0,
+        note=f"{3.0 * prompt_len * H * gd * gv / ms / 1e9:.2f} fp32 TFLOP/s of recurrence (3 ops per state element and token); "
+             "sequential in time, parallel over heads and value columns")
+    state8 = torch.zeros(8, H, gd, gv, device=dev)
+    yg8 = yg[:8].contiguous()
+    ms1 = t.kernel(lambda: SK.gla_scan(yg8, 0, H * gd, 2 * H * gd, 2 * H * gd + 2 * H * gv, a2, a2b, state8, zero,
+                                       torch.zeros(8, dtype=torch.int32, device=dev), 8, 1, H, gd, gv, gd ** -0.5, 16.0))
+    add("gla_scan_kernel, one token, batch 8", ms1, "(none)", 0.0, nbytes=2.0 * state8.numel() * 4,
+        note="reads and writes the fp32 state once")
+    o = torch.randn(prompt_len, H * gv, device=dev)
+    add("headnorm_gate_kernel", t.kernel(lambda: SK.headnorm_gate(o, torch.ones(gv, **bf), yg[:, :H * gv], H, gv, 1e-5)),
+        "swiglu_kernel", t.kernel(lambda: K.swiglu(torch.randn(prompt_len, 2 * H * gv, **bf))), nbytes=prompt_len * H * gv * (4 + 4 + 2))
+    return rows
+
+
+def run(sizes: List[str], prompt_len: int = 2048, steps: int = 64, warmup: int = 8, batches: List[int] = (1, 8),
+        kernels: bool = True) -> Dict[str, Any]:
+    from ..models.engine import B200Engine
+    from ..models.hybrid_engine import HybridEngine
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+        peaks = {"hbm_gbs": float(m["hbm_gbs"]), "bf16_tflops": float(m["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        pass
+    result: Dict[str, Any] = {"metric": "folirax_vs_llama_equal_size", "data": "synthetic", "dtype": "bf16", "peaks": peaks,
+                              "prompt_len": prompt_len, "steps": steps, "warmup": warmup, "sizes": {}}
+    for name in sizes:
+        s = SIZES[name]
+        entry: Dict[str, Any] = {"shape": s}
+        fcfg = folirax_config(s)
+        eng = HybridEngine.random_init(fcfg, dev, seed=0)
+        entry["folirax"] = _model_times(eng, s["vocab"], prompt_len, list(batches), steps, warmup)
+        del eng
+        torch.cuda.empty_cache()
+        leng = B200Engine.random_init(llama_config(s), dev, seed=0)
+        entry["llama"] = _model_times(leng, s["vocab"], prompt_len, list(batches), steps, warmup)
+        del leng
+        torch.cuda.empty_cache()
+        if kernels:
+            entry["kernels"] = _kernel_table(s, dev, peaks, prompt_len)
+        result["sizes"][name] = entry
+    return result

@@ -119,10 +119,11 @@ def test_linear_paths(dtype, shape):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("layers", [[gla()], [gla(heads=1, dim=80, vdim=8, tau=1.0)], [gla(heads=3, dim=48, vdim=40, tau=64.0, mlp=ff(24))],
+                                    [gla(heads=1, dim=272, vdim=6, tau=4.0)],
                                     [attn()], [attn(heads=2, kv_heads=2, dim=16, vdim=16, rot=16, mlp=ff(32))],
                                     [attn(heads=6, kv_heads=1, dim=40, vdim=72, rot=2, scale=1.0)],
                                     [attn(), attn(kv_from=0)]],
-                         ids=["gla", "gla-wide-key-tau1", "gla-3h-mlp", "attn-gqa", "attn-full-rot-mlp", "attn-mqa-rot2", "attn-shared-kv"])
+                         ids=["gla", "gla-wide-key-tau1", "gla-3h-mlp", "gla-key272", "attn-gqa", "attn-full-rot-mlp", "attn-mqa-rot2", "attn-shared-kv"])
 def test_single_mechanism_models(dtype, layers):
     cfg = config(layers)
     eng, cpu = build(cfg, dtype, seed=3)
@@ -182,17 +183,14 @@ def test_decode_matches_prefill_and_oracle(dtype, prompt):
         assert err(torch.stack(rows), whole[prompt:]) < 5e-5
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_unequal_batch_equals_each_alone(dtype):
-    """Left-padded batch of prompts of 1, 7 and 40 tokens, then decoded together: every row equals the request alone
-    (padding must touch neither the recurrent state nor the visible keys nor the positions)."""
-    cfg = config(MIXED)
-    eng, cpu = build(cfg, dtype, seed=6)
-    lens, extra = [1, 7, 40], 36
+def run_unequal_batch(cfg, dtype, lens, extra, seed):
+    """Left-padded batch of prompts of the given lengths, then `extra` tokens decoded together; every row is compared
+    with the oracle run of that request alone."""
+    eng, cpu = build(cfg, dtype, seed=seed)
     seqs = [tokens(n + extra, cfg.vocab_size, 20 + n) for n in lens]
-    S = max(lens)
-    ids = torch.zeros((3, S), dtype=torch.long)
-    mask = torch.zeros((3, S), dtype=torch.int32)
+    S, B = max(lens), len(lens)
+    ids = torch.zeros((B, S), dtype=torch.long)
+    mask = torch.zeros((B, S), dtype=torch.int32)
     rows = []
     for b, (n, s) in enumerate(zip(lens, seqs)):
         ids[b, S - n:] = torch.tensor(s[:n])
@@ -212,6 +210,22 @@ def test_unequal_batch_equals_each_alone(dtype):
         assert err(got_prompt[at:at + n], want[:n]) < TOL[dtype], b
         assert err(torch.stack([x[b] for x in steps]), want[n:]) < TOL[dtype], b
         at += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_batch_equals_each_alone(dtype):
+    """Prompts of 1, 7 and 40 tokens in one batch: padding must touch neither the recurrent state nor the visible keys
+    nor the positions."""
+    run_unequal_batch(config(MIXED), dtype, [1, 7, 40], 36, seed=6)
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+def test_wide_heads_on_the_shared_attention_kernels(dim):
+    """64- and 128-wide heads in bfloat16 run the tcgen05 / split-KV attention kernels the LLaMA models use, with this
+    design's score scale, unit-norm q / k, gates and shared keys around them: unequal batch across the 128-query tiles."""
+    a = dict(heads=4, kv_heads=2, dim=dim, vdim=dim, rot=dim // 2, scale=0.11)
+    cfg = config([attn(**a), gla(), attn(**a, kv_from=0, mlp=ff(64))], width=128)
+    run_unequal_batch(cfg, torch.bfloat16, [5, 150, 131], 40, seed=13)
 
 
 def test_state_and_cache_are_clean_when_used_again():
