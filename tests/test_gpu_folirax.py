@@ -219,6 +219,23 @@ def test_unequal_batch_equals_each_alone(dtype):
     run_unequal_batch(config(MIXED), dtype, [1, 7, 40], 36, seed=6)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_odd_sizes_and_a_batch_of_ten(dtype):
+    """Sizes that fit no vector width or tile (width 90, heads of 10 / 14 / 12 channels, 3 query heads on 1 key head, vocab
+    77) in a batch of ten unequal requests: more rows than the weight-streaming kernel takes, so decoding runs the GEMMs."""
+    layers = [attn(heads=3, kv_heads=1, dim=10, vdim=14, rot=6, scale=0.4, mlp=ff(50)), gla(heads=3, dim=12, vdim=10, tau=3.0),
+              attn(heads=3, kv_heads=1, dim=10, vdim=14, rot=6, scale=0.4, kv_from=0)]
+    cfg = config(layers, vocab=77, width=90)
+    run_unequal_batch(cfg, dtype, [3, 17, 1, 9, 30, 2, 12, 25, 8, 21], 12, seed=17)
+
+
+@pytest.mark.parametrize("prompt", [2, 9])
+def test_wide_heads_short_prompts(prompt):
+    a = dict(heads=2, kv_heads=1, dim=128, vdim=128, rot=64, scale=0.09)
+    cfg = config([attn(**a), attn(**a, kv_from=0, mlp=ff(64))], width=128)
+    run_unequal_batch(cfg, torch.bfloat16, [prompt], 5, seed=19)
+
+
 @pytest.mark.parametrize("dim", [64, 128])
 def test_wide_heads_on_the_shared_attention_kernels(dim):
     """64- and 128-wide heads in bfloat16 run the tcgen05 / split-KV attention kernels the LLaMA models use, with this
