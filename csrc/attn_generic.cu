@@ -5,9 +5,10 @@
 //    the rest pass through), then optional weight-free unit-RMS scaling of q and k per head, append of k / v to the
 //    cache [B][G][T][D] / [B][G][T][Dv].  Token (b, s) goes to slot *cache_len + s at position slot - pad_left[b].
 //    A layer that reads another layer's keys and values runs it for the queries only.
-//  * attn_rows_kernel   — one warp per query: blocks of 32 keys (one key per lane for the scores, one value column per
-//    lane for the output), online softmax in fp32, causal over slots [pad_left[b], slot], optional per-head output
-//    gate sigmoid(g).  Prompts of any length; exact fall-back for head sizes the tensor-core kernels are not built for.
+//  * attn_rows_kernel   — 16 queries of one head per CTA against key / value tiles of 32 rows staged in shared memory
+//    (one key per lane for the scores, one value column per lane for the output), online softmax in fp32, causal over
+//    slots [pad_left[b], slot], optional per-head output gate sigmoid(g).  Prompts of any length; exact path for
+//    float32 and for head sizes the tensor-core kernels are not built for.
 //  * attn_decode_kernel — one CTA per (row, head) for a single new token: its warps take interleaved blocks of 32 keys
 //    and merge their (max, sum, output) triples in shared memory.
 //
@@ -118,32 +119,128 @@ __device__ __forceinline__ void attn_block(const float* __restrict__ qs, const T
   }
 }
 
+// Rows j0 .. j0+31 of a cache head (row length n, rows beyond jmax read as zero) into shared memory as fp32 with row
+// pitch `pitch`; 16-byte global loads when a row is a whole number of them, else element by element (which also zeroes
+// the columns between n and the next multiple of four, the part of the pitch the dot products read).
 template <typename T>
-__global__ void __launch_bounds__(128) attn_rows_kernel(AttnParams p, const T* __restrict__ q, const T* __restrict__ kc,
-                                                        const T* __restrict__ vc, T* __restrict__ out) {
-  extern __shared__ float smem[];                       // [warps][D] queries in fp32
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int s = blockIdx.x * nw + warp;
-  if (s >= p.S) return;
-  const int m = b * p.S + s;
+__device__ __forceinline__ void stage_rows(float* dst, int pitch, const T* __restrict__ src, int n, int j0, int jmax) {
+  constexpr int VN = 16 / sizeof(T);
+  if (n % VN == 0 && ((uintptr_t)src & 15) == 0) {
+    const int per_row = n / VN;
+    for (int i = threadIdx.x; i < 32 * per_row; i += blockDim.x) {
+      const int r = i / per_row, cv = i % per_row, j = j0 + r;
+      float* d = dst + r * pitch + cv * VN;
+      if (j <= jmax) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)j * n + cv * VN);
+        if constexpr (sizeof(T) == 2) {
+          *reinterpret_cast<float4*>(d) = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+          *reinterpret_cast<float4*>(d + 4) = make_float4(bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w));
+        } else {
+          *reinterpret_cast<uint4*>(d) = raw;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VN; e += 4) *reinterpret_cast<float4*>(d + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    return;
+  }
+  const int np = (n + 3) & ~3;
+  for (int i = threadIdx.x; i < 32 * np; i += blockDim.x) {
+    const int r = i / np, c = i % np, j = j0 + r;
+    dst[r * pitch + c] = (j <= jmax && c < n) ? to_f(src[(size_t)j * n + c]) : 0.0f;
+  }
+}
+
+// Prompt attention, tiled: a CTA owns AR_QB consecutive queries of one head (AR_QW per warp) and walks the visible keys
+// in tiles of 32.  The K and V rows of a tile are brought into shared memory once, with coalesced loads, converted to
+// fp32, and serve all the CTA's queries; a lane scores one key (16-byte shared-memory reads of its K row against the
+// query held in shared memory), then owns value columns lane, lane + 32, ... for the weighted sum.
+constexpr int AR_WARPS = 4, AR_QW = 4, AR_QB = AR_WARPS * AR_QW;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, const T* __restrict__ q, const T* __restrict__ kc,
+                                                                  const T* __restrict__ vc, T* __restrict__ out) {
+  extern __shared__ float4 smem4[];
+  float* smem = reinterpret_cast<float*>(smem4);
+  const int DP = ((p.D + 3) & ~3) + 4;                   // fp32 pitch of a K / q row: 16-byte rows, banks spread
+  float* Qs = smem;                                      // [AR_QB][DP]
+  float* Ks = Qs + AR_QB * DP;                           // [32][DP]
+  float* Vs = Ks + 32 * DP;                              // [32][DVP]
+  const int DVP = (p.Dv + 3) & ~3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z, q0 = blockIdx.x * AR_QB;
   const int g = h / (p.H / p.G);
-  float* qs = smem + warp * p.D;
-  const T* qr = q + ((size_t)m * p.H + h) * p.D;
-  for (int c = lane; c < p.D; c += 32) qs[c] = to_f(qr[c]);
-  __syncwarp();
+  const int base = p.cache_len ? *p.cache_len : 0;
   const int lo = p.pad_left ? p.pad_left[b] : 0;
-  const int hi = (p.cache_len ? *p.cache_len : 0) + s;   // own slot: the last visible key
+  const int hi_cta = base + min(q0 + AR_QB, p.S) - 1;    // last key any query of this CTA sees
+  for (int i = threadIdx.x; i < AR_QB * DP; i += blockDim.x) {
+    const int r = i / DP, c = i % DP, s = q0 + r;
+    Qs[i] = (s < p.S && c < p.D) ? to_f(q[((size_t)(b * p.S + s) * p.H + h) * p.D + c]) : 0.0f;
+  }
   const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.D;
   const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.Dv;
-  float mrun = -INFINITY, lrun = 0.0f, acc[AT_MAXV] = {};
-  for (int j0 = lo & ~31; j0 <= hi; j0 += 32) attn_block<T>(qs, kbase, vbase, j0, lo, hi, p.D, p.Dv, p.scale, mrun, lrun, acc);
-  float gmul = lrun > 0.0f ? 1.0f / lrun : 0.0f;         // a padding query sees nothing: its row is zero
-  if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)m * p.ldg + h]);
+  float mrun[AR_QW], lrun[AR_QW], acc[AR_QW][NV];
 #pragma unroll
-  for (int i = 0; i < AT_MAXV; ++i) {
-    const int c = lane + 32 * i;
-    if (c < p.Dv) out[((size_t)m * p.H + h) * p.Dv + c] = from_f<T>(acc[i] * gmul);
+  for (int qi = 0; qi < AR_QW; ++qi) {
+    mrun[qi] = -INFINITY; lrun[qi] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) acc[qi][i] = 0.0f;
+  }
+  for (int j0 = lo & ~31; j0 <= hi_cta; j0 += 32) {
+    __syncthreads();                                     // the previous tile is no longer read
+    stage_rows<T>(Ks, DP, kbase, p.D, j0, hi_cta);
+    stage_rows<T>(Vs, DVP, vbase, p.Dv, j0, hi_cta);
+    __syncthreads();
+#pragma unroll
+    for (int qi = 0; qi < AR_QW; ++qi) {
+      const int s = q0 + warp * AR_QW + qi;
+      const int hi = base + s;
+      if (s >= p.S || j0 > hi) continue;                 // warp-uniform
+      const int j = j0 + lane;
+      float sc = -INFINITY;
+      if (j >= lo && j <= hi) {
+        const float4* kr = reinterpret_cast<const float4*>(Ks + lane * DP);
+        const float4* qr = reinterpret_cast<const float4*>(Qs + (warp * AR_QW + qi) * DP);
+        float d0 = 0.0f, d1 = 0.0f;
+        for (int c = 0; c < (DP - 4) / 4; ++c) {
+          const float4 a = qr[c], k4 = kr[c];
+          d0 = fmaf(a.x, k4.x, d0); d1 = fmaf(a.y, k4.y, d1); d0 = fmaf(a.z, k4.z, d0); d1 = fmaf(a.w, k4.w, d1);
+        }
+        sc = (d0 + d1) * p.scale;
+      }
+      const float mnew = fmaxf(mrun[qi], warp_max(sc));
+      if (mnew == -INFINITY) continue;
+      const float corr = mrun[qi] == -INFINITY ? 0.0f : expf(mrun[qi] - mnew);
+      const float pj = sc == -INFINITY ? 0.0f : expf(sc - mnew);
+      lrun[qi] = lrun[qi] * corr + warp_sum(pj);
+      mrun[qi] = mnew;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) acc[qi][i] *= corr;
+      const int jend = min(32, hi - j0 + 1);
+      for (int t = 0; t < jend; ++t) {
+        const float pt = __shfl_sync(0xffffffffu, pj, t);
+        const float* vr = Vs + t * DVP;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c = lane + 32 * i;
+          if (c < p.Dv) acc[qi][i] = fmaf(pt, vr[c], acc[qi][i]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int qi = 0; qi < AR_QW; ++qi) {
+    const int s = q0 + warp * AR_QW + qi;
+    if (s >= p.S) continue;
+    const int m = b * p.S + s;
+    float gmul = lrun[qi] > 0.0f ? 1.0f / lrun[qi] : 0.0f;      // a padding query sees nothing: its row is zero
+    if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)m * p.ldg + h]);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < p.Dv) out[((size_t)m * p.H + h) * p.Dv + c] = from_f<T>(acc[qi][i] * gmul);
+    }
   }
 }
 
@@ -189,6 +286,119 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(AttnParams p
   }
 }
 
+// One new token, split over the keys: a CTA owns one key/value head of one row and every `splits`-th tile of 32 keys;
+// the tile is staged in shared memory once and serves all query heads of the group (a warp takes up to AS_RW of them).
+// Each CTA leaves an unnormalised (max, sum, output) triple per query head; attn_merge_kernel joins the splits,
+// normalises, applies the output gate and stores.  Contexts of thousands of keys thus spread over the whole GPU.
+constexpr int AS_WARPS = 4, AS_RW = 4;             // query heads per group <= AS_WARPS * AS_RW
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p, const T* __restrict__ q, const T* __restrict__ kc,
+                                                                   const T* __restrict__ vc, float* __restrict__ part, int splits) {
+  extern __shared__ float4 smem4[];
+  float* smem = reinterpret_cast<float*>(smem4);
+  const int R = p.H / p.G;
+  const int DP = ((p.D + 3) & ~3) + 4;
+  float* Qs = smem;                                      // [R][DP]
+  float* Ks = Qs + R * DP;                               // [32][DP]
+  float* Vs = Ks + 32 * DP;                              // [32][DVP]
+  const int DVP = (p.Dv + 3) & ~3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int lo = p.pad_left ? p.pad_left[b] : 0;
+  const int hi = p.cache_len ? *p.cache_len : 0;         // the new token's own slot
+  for (int i = threadIdx.x; i < R * DP; i += blockDim.x) {
+    const int r = i / DP, c = i % DP;
+    Qs[i] = c < p.D ? to_f(q[((size_t)b * p.H + g * R + r) * p.D + c]) : 0.0f;
+  }
+  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.D;
+  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.Dv;
+  float mrun[AS_RW], lrun[AS_RW], acc[AS_RW][NV];
+#pragma unroll
+  for (int qi = 0; qi < AS_RW; ++qi) {
+    mrun[qi] = -INFINITY; lrun[qi] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) acc[qi][i] = 0.0f;
+  }
+  for (int j0 = (lo & ~31) + 32 * z; j0 <= hi; j0 += 32 * splits) {
+    __syncthreads();
+    stage_rows<T>(Ks, DP, kbase, p.D, j0, hi);
+    stage_rows<T>(Vs, DVP, vbase, p.Dv, j0, hi);
+    __syncthreads();
+    const int j = j0 + lane;
+    const bool vis = j >= lo && j <= hi;
+#pragma unroll
+    for (int qi = 0; qi < AS_RW; ++qi) {
+      const int r = warp + AS_WARPS * qi;
+      if (r >= R) continue;                              // warp-uniform
+      float sc = -INFINITY;
+      if (vis) {
+        const float4* kr = reinterpret_cast<const float4*>(Ks + lane * DP);
+        const float4* qr = reinterpret_cast<const float4*>(Qs + r * DP);
+        float d0 = 0.0f, d1 = 0.0f;
+        for (int c = 0; c < (DP - 4) / 4; ++c) {
+          const float4 a = qr[c], k4 = kr[c];
+          d0 = fmaf(a.x, k4.x, d0); d1 = fmaf(a.y, k4.y, d1); d0 = fmaf(a.z, k4.z, d0); d1 = fmaf(a.w, k4.w, d1);
+        }
+        sc = (d0 + d1) * p.scale;
+      }
+      const float mnew = fmaxf(mrun[qi], warp_max(sc));
+      if (mnew == -INFINITY) continue;
+      const float corr = mrun[qi] == -INFINITY ? 0.0f : expf(mrun[qi] - mnew);
+      const float pj = sc == -INFINITY ? 0.0f : expf(sc - mnew);
+      lrun[qi] = lrun[qi] * corr + warp_sum(pj);
+      mrun[qi] = mnew;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) acc[qi][i] *= corr;
+      const int jend = min(32, hi - j0 + 1);
+      for (int t = 0; t < jend; ++t) {
+        const float pt = __shfl_sync(0xffffffffu, pj, t);
+        const float* vr = Vs + t * DVP;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c = lane + 32 * i;
+          if (c < p.Dv) acc[qi][i] = fmaf(pt, vr[c], acc[qi][i]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int qi = 0; qi < AS_RW; ++qi) {
+    const int r = warp + AS_WARPS * qi;
+    if (r >= R) continue;
+    float* dst = part + (((size_t)b * p.H + g * R + r) * splits + z) * (p.Dv + 2);
+    if (lane == 0) { dst[0] = mrun[qi]; dst[1] = lrun[qi]; }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < p.Dv) dst[2 + c] = acc[qi][i];
+    }
+  }
+}
+
+template <typename T>
+__global__ void attn_merge_kernel(AttnParams p, const float* __restrict__ part, int splits, T* __restrict__ out) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const float* src = part + ((size_t)b * p.H + h) * splits * (p.Dv + 2);
+  float mall = -INFINITY;
+  for (int z = 0; z < splits; ++z) mall = fmaxf(mall, src[(size_t)z * (p.Dv + 2)]);
+  float lall = 0.0f;
+  for (int z = 0; z < splits; ++z) {
+    const float m = src[(size_t)z * (p.Dv + 2)];
+    if (m != -INFINITY) lall += src[(size_t)z * (p.Dv + 2) + 1] * expf(m - mall);
+  }
+  float gmul = lall > 0.0f ? 1.0f / lall : 0.0f;
+  if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)b * p.ldg + h]);
+  for (int c = threadIdx.x; c < p.Dv; c += blockDim.x) {
+    float o = 0.0f;
+    for (int z = 0; z < splits; ++z) {
+      const float m = src[(size_t)z * (p.Dv + 2)];
+      if (m != -INFINITY) o += src[(size_t)z * (p.Dv + 2) + 2 + c] * expf(m - mall);
+    }
+    out[((size_t)b * p.H + h) * p.Dv + c] = from_f<T>(o * gmul);
+  }
+}
+
 // out[m, h, :] *= sigmoid(gate[m, h]) for attention kernels that have no gate input (the tcgen05 prefill kernel)
 template <typename T>
 __global__ void head_gate_kernel(T* __restrict__ out, const float* __restrict__ gate, int ldg, int M, int H, int Dv) {
@@ -221,23 +431,58 @@ extern "C" JL_API int jl_attn_prep(const float* y, int ldy, int q_off, int k_off
   return JL_OK;
 }
 
+extern "C" JL_API int jl_attn_generic_splits(int B, int H, int G, int T_cap) {
+  if (G <= 0 || H / G > AS_WARPS * AS_RW) return 0;      // wider groups: the one-CTA-per-head kernel
+  int s = 296 / (B * G > 0 ? B * G : 1);                 // about one resident wave of CTAs
+  const int tiles = (T_cap + 63) / 64;                   // at least two key tiles per split at full capacity
+  if (s > tiles) s = tiles;
+  if (s > 64) s = 64;
+  return s < 1 ? 1 : s;
+}
+
 extern "C" JL_API int jl_attn_generic(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
                                       const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv,
-                                      int T_cap, float scale, int dtype, void* stream) {
+                                      int T_cap, float scale, float* scratch, int splits, int dtype, void* stream) {
   JL_CHECK_ARG(B >= 1 && S >= 1 && G >= 1 && H % G == 0, "jl_attn_generic: H=%d not a multiple of G=%d", H, G);
   JL_CHECK_ARG(Dv <= 32 * AT_MAXV, "jl_attn_generic: value size %d above %d", Dv, 32 * AT_MAXV);
   AttnParams p{B, S, H, G, D, Dv, T_cap, scale, cache_len, pad_left, gate, ldg};
   cudaStream_t st = (cudaStream_t)stream;
   count_launch();
-  if (S == 1) {
+  if (S == 1 && scratch != nullptr && splits >= 1 && H / G <= AS_WARPS * AS_RW) {
+    const int dp = ((D + 3) & ~3) + 4;
+    const size_t smem = (size_t)((H / G + 32) * dp + 32 * ((Dv + 3) & ~3)) * sizeof(float);
+    JL_CHECK_ARG(smem <= 200 * 1024, "jl_attn_generic: head sizes %d / %d do not fit the key tile", D, Dv);
+#define JL_AS(NV_)                                                                                                   \
+  JL_DISPATCH_DTYPE(dtype, {                                                                                         \
+    if (smem > 48 * 1024)                                                                                            \
+      JL_CUDA(cudaFuncSetAttribute(attn_split_kernel<T, NV_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    attn_split_kernel<T, NV_><<<dim3(splits, G, B), AS_WARPS * 32, smem, st>>>(p, (const T*)q, (const T*)k_cache,   \
+                                                                               (const T*)v_cache, scratch, splits);  \
+  })
+    const int nv = (Dv + 31) / 32;
+    if (nv <= 1) JL_AS(1); else if (nv <= 2) JL_AS(2); else if (nv <= 4) JL_AS(4); else if (nv <= 8) JL_AS(8); else JL_AS(16);
+#undef JL_AS
+    JL_CUDA(cudaGetLastError());
+    count_launch();
+    JL_DISPATCH_DTYPE(dtype, attn_merge_kernel<T><<<dim3(H, B), 128, 0, st>>>(p, scratch, splits, (T*)out));
+  } else if (S == 1) {
     const size_t smem = (size_t)(D + 2 * AD_WARPS + AD_WARPS * Dv) * sizeof(float);
     JL_DISPATCH_DTYPE(dtype, attn_decode_kernel<T><<<dim3(H, B), AD_WARPS * 32, smem, st>>>(p, (const T*)q, (const T*)k_cache,
                                                                                          (const T*)v_cache, (T*)out));
   } else {
-    const int nw = 4;
-    const size_t smem = (size_t)nw * D * sizeof(float);
-    JL_DISPATCH_DTYPE(dtype, attn_rows_kernel<T><<<dim3((S + nw - 1) / nw, H, B), nw * 32, smem, st>>>(
-                                 p, (const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out));
+    const int dp = ((D + 3) & ~3) + 4;
+    const size_t smem = (size_t)((AR_QB + 32) * dp + 32 * ((Dv + 3) & ~3)) * sizeof(float);
+    JL_CHECK_ARG(smem <= 200 * 1024, "jl_attn_generic: head sizes %d / %d do not fit the key tile", D, Dv);
+#define JL_AR(NV_)                                                                                                  \
+  JL_DISPATCH_DTYPE(dtype, {                                                                                        \
+    if (smem > 48 * 1024)                                                                                           \
+      JL_CUDA(cudaFuncSetAttribute(attn_rows_kernel<T, NV_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    attn_rows_kernel<T, NV_><<<dim3((S + AR_QB - 1) / AR_QB, H, B), AR_WARPS * 32, smem, st>>>(                    \
+        p, (const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out);                                             \
+  })
+    const int nv = (Dv + 31) / 32;
+    if (nv <= 1) JL_AR(1); else if (nv <= 2) JL_AR(2); else if (nv <= 4) JL_AR(4); else if (nv <= 8) JL_AR(8); else JL_AR(16);
+#undef JL_AR
   }
   JL_CUDA(cudaGetLastError());
   return JL_OK;

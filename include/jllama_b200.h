@@ -288,10 +288,13 @@ int jl_attn_prep(const float* y, int ldy, int q_off, int k_off, int v_off, void*
                  const float* cos_t, const float* sin_t, int max_pos, int rot, int unit_norm, float eps, const int* cache_len,
                  const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int dtype, void* stream);
 /* Causal softmax attention of S new tokens per row (slots *cache_len .. *cache_len+S-1) over slots [pad_left[b], own slot];
- * q [B*S, H, D], out [B*S, H, Dv]; gate (optional) fp32 [B*S, ldg], column h: out *= sigmoid(gate). */
+ * q [B*S, H, D], out [B*S, H, Dv]; gate (optional) fp32 [B*S, ldg], column h: out *= sigmoid(gate).
+ * One new token (S == 1) with `scratch` (B*H*splits*(Dv+2) floats, splits from jl_attn_generic_splits, 0 = not available for
+ * this grouping): the keys are split over `splits` CTAs per key/value head and merged by a second launch. */
+int jl_attn_generic_splits(int B, int H, int G, int T_cap);
 int jl_attn_generic(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
                     const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, float scale,
-                    int dtype, void* stream);
+                    float* scratch, int splits, int dtype, void* stream);
 /* out[m, h, :] *= sigmoid(gate[m, h]) in place. */
 int jl_head_gate(void* out, const float* gate, int ldg, int M, int H, int Dv, int dtype, void* stream);
 /* Gated linear attention scan: state [B][H][D][Dv] fp32 (in/out), o fp32 [B*S, H, Dv]; a2 [H*D, R], a2_bias [H*D] of dtype.

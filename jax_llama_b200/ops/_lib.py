@@ -63,7 +63,8 @@ _HYBRID = {
     "jl_act_inplace": (i32, [vp, i32, i32, i32, i32, f32, f32, i32, vp]),
     "jl_linear_any": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, f32, f32, i32, i32, vp]),
     "jl_attn_prep": (i32, [fp, i32, i32, i32, i32, vp, vp, vp, fp, fp, i32, i32, i32, f32, ip, ip] + [i32] * 8 + [vp]),
-    "jl_attn_generic": (i32, [vp, vp, vp, vp, fp, i32, ip, ip] + [i32] * 7 + [f32, i32, vp]),
+    "jl_attn_generic": (i32, [vp, vp, vp, vp, fp, i32, ip, ip] + [i32] * 7 + [f32, fp, i32, i32, vp]),
+    "jl_attn_generic_splits": (i32, [i32, i32, i32, i32]),
     "jl_head_gate": (i32, [vp, fp, i32, i32, i32, i32, i32, vp]),
     "jl_gla_scan": (i32, [fp, i32, i32, i32, i32, i32, vp, vp, fp, fp, ip, ip] + [i32] * 6 + [f32, f32, fp, i32, vp]),
     "jl_gla_scan_ws_floats": (sz, [i32, i32, i32, i32, i32]),

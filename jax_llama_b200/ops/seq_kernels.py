@@ -160,10 +160,16 @@ def attn_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     Dv = v_cache.shape[3]
     if out is None:
         out = torch.empty((B * S, H * Dv), dtype=q.dtype, device=q.device)
-    _lib.check(_lib.lib().jl_attn_generic(
+    L = _lib.lib()
+    splits, scratch = 0, None
+    if S == 1:                     # one new token: keys split over CTAs, partial results meet in scratch
+        splits = int(L.jl_attn_generic_splits(B, H, G, T_cap))
+        if splits:
+            scratch = torch.empty(B * H * splits * (Dv + 2), dtype=torch.float32, device=q.device)
+    _lib.check(L.jl_attn_generic(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(gate),
         gate.stride(0) if gate is not None else 0, _p(cache_len), _p(pad_left), B, S, H, G, D, Dv, T_cap, float(scale),
-        dtype_code(q.dtype), _stream()), "jl_attn_generic")
+        _p(scratch), splits, dtype_code(q.dtype), _stream()), "jl_attn_generic")
     return out
 
 

@@ -158,7 +158,7 @@ def _kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str, float],
     xp = torch.randn(prompt_len, W, **bf)
     wu = torch.randn(F, W, **bf) * 0.02
     fl = 2.0 * prompt_len * F * W
-    add("tcgen05 GEMM fp32 out + relu^2 pass (ff up)", t.kernel(lambda: SK.linear(xp, wu, act=SK.ACT_RELU2, out_f32=False)),
+    add("tcgen05 GEMM bf16 out + in-place relu^2 pass (ff up)", t.kernel(lambda: SK.linear(xp, wu, act=SK.ACT_RELU2, out_f32=False)),
         "tcgen05 GEMM bf16 out (same N, K)", t.kernel(lambda: K.linear(xp, wu)), flops=fl)
 
     # ---- norms
