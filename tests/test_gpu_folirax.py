@@ -15,6 +15,7 @@ from jax_llama_b200.generation import LLaMA                                  # n
 from jax_llama_b200.models.folirax import FoliraxForCausalLM                 # noqa: E402
 from jax_llama_b200.models.hybrid_engine import HybridEngine, random_tensors  # noqa: E402
 from jax_llama_b200.ops import seq_kernels as SK                             # noqa: E402
+from jax_llama_b200.tokenizers import IdTokenizer                            # noqa: E402
 
 from tests import folirax_oracle as O                                        # noqa: E402
 
@@ -348,17 +349,6 @@ def test_recurrent_state_keeps_a_far_token(dtype, gap):
 
 
 # ------------------------------------------------------------------------------------------ the framework's entry points
-class _IdTokenizer:
-    """Token ids as text: "3 17 5".  The generation front-end needs only encode / decode / bos / eos."""
-    bos_id, eos_id = 1, 0
-
-    def encode(self, s, bos=True, eos=False):
-        return ([self.bos_id] if bos else []) + [int(t) for t in s.split()]
-
-    def decode(self, ids):
-        return " ".join(str(i) for i in ids)
-
-
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_greedy_generation_through_the_front_end(dtype, tmp_path):
     """save_pretrained → registry → `LLaMA.generate_from_str` (left-padded batch, scheduler, on-device arg-max): every
@@ -371,7 +361,7 @@ def test_greedy_generation_through_the_front_end(dtype, tmp_path):
     assert registry.resolve(str(tmp_path))[0] == "folirax"
     loaded = registry.load_pretrained(str(tmp_path), dtype=dtype, device="cuda")
     assert isinstance(loaded, FoliraxForCausalLM) and loaded.config.to_dict() == cfg.to_dict()
-    llm = LLaMA(loaded.params, loaded, _IdTokenizer())
+    llm = LLaMA(loaded.params, loaded, IdTokenizer(cfg.vocab_size))
     prompts = ["7 8 9 10 11 12", "40", "3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3 3"]
     texts = llm.generate_from_str(prompts, max_gen_len=24, temperature=0.0)
     cpu = {k: v.cpu() for k, v in loaded.params.items()}
@@ -386,3 +376,21 @@ def test_greedy_generation_through_the_front_end(dtype, tmp_path):
             assert row[ids[j]] >= row.max() - (1e-3 if dtype == torch.float32 else 0.15), (p, j)
     sampled = llm.generate_from_str(prompts[:1], max_gen_len=8, temperature=0.9, top_p=0.9)
     assert len(sampled[0].split()) >= 7
+
+
+def test_command_line_generates_from_a_checkpoint_directory(tmp_path):
+    """examples/example.py --model_dir: registry, loader, engine, scheduler and sampler behind the command line."""
+    import os
+    import subprocess
+    import sys
+
+    cfg = config(MIXED, vocab=80)
+    FoliraxForCausalLM(cfg, seed=3, _do_init=True).save_pretrained(str(tmp_path))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "example.py"), "--model_dir", str(tmp_path), "--prompt",
+                        "7 8 9", "--prompt", "40", "--max_gen_len", "6", "--temperature", "0"], capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.strip() and not l.startswith("=")]
+    assert lines[0].split()[:4] == ["1", "7", "8", "9"] and lines[1].split()[:2] == ["1", "40"]
+    assert all(0 <= int(t) < 80 for l in lines[:2] for t in l.split())
