@@ -33,6 +33,8 @@ constexpr int AP_WARPS = 4;      // heads per CTA of the preparation kernel (one
 template <typename T>
 __global__ void __launch_bounds__(AP_WARPS * 32) attn_prep_kernel(PrepParams p, T* __restrict__ q_out, T* __restrict__ kc,
                                                                   T* __restrict__ vc, int n_heads, int pair_loads) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   const int m = blockIdx.x, head = blockIdx.y * AP_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (head >= n_heads) return;
   const int b = m / p.S, s = m % p.S;
@@ -161,6 +163,8 @@ constexpr int AR_WARPS = 4, AR_QW = 4, AR_QB = AR_WARPS * AR_QW;
 template <typename T, int NV>
 __global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, const T* __restrict__ q, const T* __restrict__ kc,
                                                                   const T* __restrict__ vc, T* __restrict__ out) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   extern __shared__ float4 smem4[];
   float* smem = reinterpret_cast<float*>(smem4);
   const int DP = ((p.D + 3) & ~3) + 4;                   // fp32 pitch of a K / q row: 16-byte rows, banks spread
@@ -249,6 +253,8 @@ constexpr int AD_WARPS = 8;
 template <typename T>
 __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(AttnParams p, const T* __restrict__ q, const T* __restrict__ kc,
                                                                     const T* __restrict__ vc, T* __restrict__ out) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   extern __shared__ float smem[];                       // [D] query | [warps][2] (max, sum) | [warps][Dv] partial outputs
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x, b = blockIdx.y;             // S == 1: row m = b
@@ -295,6 +301,8 @@ constexpr int AS_WARPS = 4, AS_RW = 4;             // query heads per group <= A
 template <typename T, int NV>
 __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p, const T* __restrict__ q, const T* __restrict__ kc,
                                                                    const T* __restrict__ vc, float* __restrict__ part, int splits) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   extern __shared__ float4 smem4[];
   float* smem = reinterpret_cast<float*>(smem4);
   const int R = p.H / p.G;
@@ -378,6 +386,8 @@ __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p,
 
 template <typename T>
 __global__ void attn_merge_kernel(AttnParams p, const float* __restrict__ part, int splits, T* __restrict__ out) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   const int h = blockIdx.x, b = blockIdx.y;
   const float* src = part + ((size_t)b * p.H + h) * splits * (p.Dv + 2);
   float mall = -INFINITY;
@@ -402,6 +412,8 @@ __global__ void attn_merge_kernel(AttnParams p, const float* __restrict__ part, 
 // out[m, h, :] *= sigmoid(gate[m, h]) for attention kernels that have no gate input (the tcgen05 prefill kernel)
 template <typename T>
 __global__ void head_gate_kernel(T* __restrict__ out, const float* __restrict__ gate, int ldg, int M, int H, int Dv) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   const size_t total = (size_t)M * H * Dv;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t mh = i / Dv;
@@ -424,8 +436,7 @@ extern "C" JL_API int jl_attn_prep(const float* y, int ldy, int q_off, int k_off
   const int n_heads = k_off >= 0 ? H + 2 * G : H;
   const int pair_loads = D % 2 == 0 && ldy % 2 == 0 && q_off % 2 == 0 && (k_off < 0 || k_off % 2 == 0) && (uintptr_t)y % 8 == 0;
   dim3 grid(B * S, (n_heads + AP_WARPS - 1) / AP_WARPS);
-  count_launch();
-  JL_DISPATCH_DTYPE(dtype, attn_prep_kernel<T><<<grid, AP_WARPS * 32, 0, (cudaStream_t)stream>>>(p, (T*)q_out, (T*)k_cache,
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(attn_prep_kernel<T>, dim3(grid), dim3(AP_WARPS * 32), 0, (cudaStream_t)stream, p, (T*)q_out, (T*)k_cache,
                                                                                                 (T*)v_cache, n_heads, pair_loads));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
@@ -447,7 +458,6 @@ extern "C" JL_API int jl_attn_generic(const void* q, const void* k_cache, const 
   JL_CHECK_ARG(Dv <= 32 * AT_MAXV, "jl_attn_generic: value size %d above %d", Dv, 32 * AT_MAXV);
   AttnParams p{B, S, H, G, D, Dv, T_cap, scale, cache_len, pad_left, gate, ldg};
   cudaStream_t st = (cudaStream_t)stream;
-  count_launch();
   if (S == 1 && scratch != nullptr && splits >= 1 && H / G <= AS_WARPS * AS_RW) {
     const int dp = ((D + 3) & ~3) + 4;
     const size_t smem = (size_t)((H / G + 32) * dp + 32 * ((Dv + 3) & ~3)) * sizeof(float);
@@ -456,18 +466,17 @@ extern "C" JL_API int jl_attn_generic(const void* q, const void* k_cache, const 
   JL_DISPATCH_DTYPE(dtype, {                                                                                         \
     if (smem > 48 * 1024)                                                                                            \
       JL_CUDA(cudaFuncSetAttribute(attn_split_kernel<T, NV_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    attn_split_kernel<T, NV_><<<dim3(splits, G, B), AS_WARPS * 32, smem, st>>>(p, (const T*)q, (const T*)k_cache,   \
+    JL_LAUNCH_PDL((attn_split_kernel<T, NV_>), dim3(dim3(splits, G, B)), dim3(AS_WARPS * 32), smem, st, p, (const T*)q, (const T*)k_cache,   \
                                                                                (const T*)v_cache, scratch, splits);  \
   })
     const int nv = (Dv + 31) / 32;
     if (nv <= 1) JL_AS(1); else if (nv <= 2) JL_AS(2); else if (nv <= 4) JL_AS(4); else if (nv <= 8) JL_AS(8); else JL_AS(16);
 #undef JL_AS
     JL_CUDA(cudaGetLastError());
-    count_launch();
-    JL_DISPATCH_DTYPE(dtype, attn_merge_kernel<T><<<dim3(H, B), 128, 0, st>>>(p, scratch, splits, (T*)out));
+      JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(attn_merge_kernel<T>, dim3(dim3(H, B)), dim3(128), 0, st, p, scratch, splits, (T*)out));
   } else if (S == 1) {
     const size_t smem = (size_t)(D + 2 * AD_WARPS + AD_WARPS * Dv) * sizeof(float);
-    JL_DISPATCH_DTYPE(dtype, attn_decode_kernel<T><<<dim3(H, B), AD_WARPS * 32, smem, st>>>(p, (const T*)q, (const T*)k_cache,
+    JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(attn_decode_kernel<T>, dim3(dim3(H, B)), dim3(AD_WARPS * 32), smem, st, p, (const T*)q, (const T*)k_cache,
                                                                                          (const T*)v_cache, (T*)out));
   } else {
     const int dp = ((D + 3) & ~3) + 4;
@@ -477,7 +486,7 @@ extern "C" JL_API int jl_attn_generic(const void* q, const void* k_cache, const 
   JL_DISPATCH_DTYPE(dtype, {                                                                                        \
     if (smem > 48 * 1024)                                                                                           \
       JL_CUDA(cudaFuncSetAttribute(attn_rows_kernel<T, NV_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    attn_rows_kernel<T, NV_><<<dim3((S + AR_QB - 1) / AR_QB, H, B), AR_WARPS * 32, smem, st>>>(                    \
+    JL_LAUNCH_PDL((attn_rows_kernel<T, NV_>), dim3(dim3((S + AR_QB - 1) / AR_QB, H, B)), dim3(AR_WARPS * 32), smem, st,                     \
         p, (const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out);                                             \
   })
     const int nv = (Dv + 31) / 32;
@@ -492,8 +501,7 @@ extern "C" JL_API int jl_head_gate(void* out, const float* gate, int ldg, int M,
   JL_CHECK_ARG(M >= 1 && H >= 1 && Dv >= 1, "jl_head_gate: bad shape");
   const size_t total = (size_t)M * H * Dv;
   const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-  count_launch();
-  JL_DISPATCH_DTYPE(dtype, head_gate_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, gate, ldg, M, H, Dv));
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(head_gate_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out, gate, ldg, M, H, Dv));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

@@ -43,6 +43,8 @@ __device__ __forceinline__ float log_sigmoid(float z) {
 
 template <typename T>
 __global__ void __launch_bounds__(GS_THREADS, 3) gla_scan_kernel(GlaParams p, const T* __restrict__ a2, const T* __restrict__ a2b) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   extern __shared__ float4 smem4[];
   float* smem = reinterpret_cast<float*>(smem4);
   const int P = p.P;                                         // lanes per value column (power of two, adjacent lanes of a warp)
@@ -150,6 +152,8 @@ __host__ __device__ inline int gla_record_floats(int P, int DP, int Dv) { return
 template <typename T>
 __global__ void __launch_bounds__(128) gla_prep_kernel(GlaParams p, const T* __restrict__ a2, const T* __restrict__ a2b,
                                                        float* __restrict__ rec, int DP) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   extern __shared__ float zs[];                                 // [R]
   const int m = blockIdx.x;
   const float* yr = p.y + (size_t)m * p.ldy;
@@ -188,6 +192,8 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 
 template <int DP, int C>
 __global__ void __launch_bounds__(GS_THREADS, 2) gla_stream_kernel(GlaParams p, const float* __restrict__ rec) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   extern __shared__ float4 smem4[];
   float* smem = reinterpret_cast<float*>(smem4);
   constexpr int PITCH = DP + 4;
@@ -299,6 +305,8 @@ __global__ void __launch_bounds__(GS_THREADS, 2) gla_stream_kernel(GlaParams p, 
 // Between the two passes: walk the chunks of a row in order.  cstate[c] holds the chunk's local end state on entry and the
 // state the chunk starts from on exit; the row's state is advanced to the end of the prompt.
 __global__ void gla_combine_kernel(GlaParams p) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   const size_t per_row = (size_t)p.H * p.D * p.Dv, total = (size_t)p.B * per_row;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t b = i / per_row, e = i % per_row, hd = e / p.Dv;           // hd = h * D + d
@@ -361,8 +369,7 @@ extern "C" JL_API int jl_gla_scan(const float* y, int ldy, int q_off, int k_off,
     JL_CHECK_ARG(t.P <= 32, "jl_gla_scan: key size %d above %d", D, 32 * t.DP);
     p.P = t.P;
     const int tcols = GS_THREADS / t.P * t.C;
-    count_launch();
-    JL_DISPATCH_DTYPE(dtype, gla_prep_kernel<T><<<B * S, 128, R * sizeof(float), st>>>(p, (const T*)a2, (const T*)a2_bias, ws, t.DP));
+      JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(gla_prep_kernel<T>, dim3(B * S), dim3(128), R * sizeof(float), st, p, (const T*)a2, (const T*)a2_bias, ws, t.DP));
     JL_CUDA(cudaGetLastError());
     const size_t smem2 = (size_t)2 * GS_TS * (3 * t.P * (t.DP + 4) + tcols) * sizeof(float);
     JL_CHECK_ARG(smem2 <= 200 * 1024, "jl_gla_scan: key size %d does not fit the pipeline stages", D);
@@ -378,25 +385,22 @@ extern "C" JL_API int jl_gla_scan(const float* y, int ldy, int q_off, int k_off,
       JL_CUDA(cudaFuncSetAttribute(gla_stream_kernel<32, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
     for (int pass = 0; pass < (nc > 1 ? 2 : 1); ++pass) {
       p.mode = nc > 1 ? (pass == 0 ? 1 : 3) : 0;
-      count_launch();
-      if (t.DP == 8) gla_stream_kernel<8, 4><<<grid2, block, smem2, st>>>(p, ws);
-      else gla_stream_kernel<32, 1><<<grid2, block, smem2, st>>>(p, ws);
+          if (t.DP == 8) JL_LAUNCH_PDL((gla_stream_kernel<8, 4>), dim3(grid2), dim3(block), smem2, st, p, ws);
+      else JL_LAUNCH_PDL((gla_stream_kernel<32, 1>), dim3(grid2), dim3(block), smem2, st, p, ws);
       JL_CUDA(cudaGetLastError());
       if (pass == 0 && nc > 1) {
         const size_t total = (size_t)B * H * D * Dv;
-        count_launch();
-        gla_combine_kernel<<<(unsigned)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184), 256, 0, st>>>(p);
+              JL_LAUNCH_PDL(gla_combine_kernel, dim3((unsigned)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184)), dim3(256), 0, st, p);
         JL_CUDA(cudaGetLastError());
       }
     }
     return JL_OK;
   }
-  count_launch();
   if (smem > 48 * 1024) {
     if (dtype == DT_BF16) JL_CUDA(cudaFuncSetAttribute(gla_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     else JL_CUDA(cudaFuncSetAttribute(gla_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
-  JL_DISPATCH_DTYPE(dtype, gla_scan_kernel<T><<<grid, block, smem, (cudaStream_t)stream>>>(p, (const T*)a2, (const T*)a2_bias));
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(gla_scan_kernel<T>, dim3(grid), dim3(block), smem, (cudaStream_t)stream, p, (const T*)a2, (const T*)a2_bias));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

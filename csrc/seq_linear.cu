@@ -37,6 +37,8 @@ template <typename T, typename OutT, int M>
 __global__ void __launch_bounds__(LR_WARPS * 32) linear_rows_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w,
                                                                     OutT* __restrict__ out, int ldo, int N, int K, int act,
                                                                     float p0, float p1, int vec_ok) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   __shared__ float red[LR_WARPS][LR_ROWS][M];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n0 = blockIdx.x * LR_ROWS;
@@ -99,6 +101,8 @@ template <typename T, typename OutT>
 __global__ void __launch_bounds__(256) linear_tiled_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w,
                                                            OutT* __restrict__ out, int ldo, int M, int N, int K, int act,
                                                            float p0, float p1) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   __shared__ float xs[LT_BK][LT_BM + 4];
   __shared__ float ws[LT_BK][LT_BN + 4];
   const int m0 = blockIdx.y * LT_BM, n0 = blockIdx.x * LT_BN;
@@ -139,21 +143,20 @@ __global__ void __launch_bounds__(256) linear_tiled_kernel(const T* __restrict__
 template <typename T, typename OutT>
 static int launch_linear(const void* x, int ldx, const void* w, void* out, int ldo, int M, int N, int K, int act, float p0,
                          float p1, cudaStream_t st) {
-  count_launch();
   if (M <= LR_MAXM) {
     constexpr int VN = Vec<T>::N;
     const int vec_ok = (K % VN == 0) && (ldx % VN == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0);
     const int blocks = (N + LR_ROWS - 1) / LR_ROWS;
 #define JL_LR(MM)                                                                                                       \
   case MM:                                                                                                              \
-    linear_rows_kernel<T, OutT, MM><<<blocks, LR_WARPS * 32, 0, st>>>((const T*)x, ldx, (const T*)w, (OutT*)out, ldo, N, K, act, \
+    JL_LAUNCH_PDL((linear_rows_kernel<T, OutT, MM>), dim3(blocks), dim3(LR_WARPS * 32), 0, st, (const T*)x, ldx, (const T*)w, (OutT*)out, ldo, N, K, act, \
                                                                    p0, p1, vec_ok);                                     \
     break;
     switch (M) { JL_LR(1) JL_LR(2) JL_LR(3) JL_LR(4) JL_LR(5) JL_LR(6) JL_LR(7) JL_LR(8) }
 #undef JL_LR
   } else {
     dim3 grid((N + LT_BN - 1) / LT_BN, (M + LT_BM - 1) / LT_BM);
-    linear_tiled_kernel<T, OutT><<<grid, 256, 0, st>>>((const T*)x, ldx, (const T*)w, (OutT*)out, ldo, M, N, K, act, p0, p1);
+    JL_LAUNCH_PDL((linear_tiled_kernel<T, OutT>), dim3(grid), dim3(256), 0, st, (const T*)x, ldx, (const T*)w, (OutT*)out, ldo, M, N, K, act, p0, p1);
   }
   return cudaGetLastError() == cudaSuccess ? JL_OK : JL_ERR_CUDA;
 }

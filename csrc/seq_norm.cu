@@ -10,6 +10,8 @@ namespace jl {
 template <typename T>
 __global__ void embed_f32_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int W,
                                  int V) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   const int m = blockIdx.x;
   int id = ids[m];
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);
@@ -21,6 +23,8 @@ __global__ void embed_f32_kernel(const int* __restrict__ ids, const T* __restric
 template <typename T>
 __global__ void norm_f32_kernel(const float* __restrict__ x, const T* __restrict__ w, T* __restrict__ out, int W, float eps,
                                 float offset) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   __shared__ float red[33];
   const float* xr = x + (size_t)blockIdx.x * W;
   float ss = 0.0f;
@@ -34,6 +38,8 @@ __global__ void norm_f32_kernel(const float* __restrict__ x, const T* __restrict
 template <typename T>
 __global__ void postnorm_add_kernel(const float* __restrict__ y, int ldy, const T* __restrict__ w_post, float* __restrict__ x,
                                     const T* __restrict__ w_next, T* __restrict__ h, int W, float eps, float offset) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   __shared__ float red[33];
   const float* yr = y + (size_t)blockIdx.x * ldy;
   float* xr = x + (size_t)blockIdx.x * W;
@@ -73,6 +79,8 @@ template <typename T, int VPT>
 __global__ void __launch_bounds__(256) postnorm_add_vec_kernel(const float* __restrict__ y, int ldy, const T* __restrict__ w_post,
                                                                float* __restrict__ x, const T* __restrict__ w_next,
                                                                T* __restrict__ h, int W, float eps, float offset) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   __shared__ float red[33];
   const float* yr = y + (size_t)blockIdx.x * ldy;
   float* xr = x + (size_t)blockIdx.x * W;
@@ -121,6 +129,8 @@ __global__ void __launch_bounds__(256) postnorm_add_vec_kernel(const float* __re
 template <typename T>
 __global__ void headnorm_gate_kernel(const float* __restrict__ o, const T* __restrict__ w, const float* __restrict__ gate,
                                      int ldg, T* __restrict__ out, int M, int H, int V, float eps, int gate_act) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (wid >= M * H) return;
   const int m = wid / H, hh = wid % H;
@@ -137,6 +147,8 @@ __global__ void headnorm_gate_kernel(const float* __restrict__ o, const T* __res
 template <typename OutT>
 __global__ void act_cast_kernel(const float* __restrict__ in, int ldi, OutT* __restrict__ out, int ldo, int M, int N, int act,
                                 float p0, float p1) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   const size_t total = (size_t)M * N;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t m = idx / N, n = idx % N;
@@ -147,6 +159,8 @@ __global__ void act_cast_kernel(const float* __restrict__ in, int ldi, OutT* __r
 // data[m, n] = act(data[m, n]) in place, 16 bytes per thread and step where the pitch allows
 template <typename T>
 __global__ void act_inplace_kernel(T* __restrict__ data, int ld, int M, int N, int act, float p0, float p1, int vec) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
   constexpr int VN = 16 / sizeof(T);
   if (vec) {
     const size_t per_row = N / VN, total = (size_t)M * per_row;
@@ -177,16 +191,14 @@ extern "C" JL_API int jl_act_inplace(void* data, int ld, int M, int N, int act, 
   const int vec = N % vn == 0 && ld % vn == 0 && (uintptr_t)data % 16 == 0;
   const size_t work = (size_t)M * N / (vec ? vn : 1);
   const int blocks = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
-  count_launch();
-  JL_DISPATCH_DTYPE(dtype, act_inplace_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)data, ld, M, N, act, p0, p1, vec));
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(act_inplace_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)data, ld, M, N, act, p0, p1, vec));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }
 
 extern "C" JL_API int jl_embed_f32(const int* ids, const void* table, float* out, int M, int W, int V, int dtype, void* stream) {
   JL_CHECK_ARG(M >= 1 && W >= 1 && V >= 1, "jl_embed_f32: bad shape M=%d W=%d V=%d", M, W, V);
-  count_launch();
-  JL_DISPATCH_DTYPE(dtype, embed_f32_kernel<T><<<M, 128, 0, (cudaStream_t)stream>>>(ids, (const T*)table, out, W, V));
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(embed_f32_kernel<T>, dim3(M), dim3(128), 0, (cudaStream_t)stream, ids, (const T*)table, out, W, V));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }
@@ -194,8 +206,7 @@ extern "C" JL_API int jl_embed_f32(const int* ids, const void* table, float* out
 extern "C" JL_API int jl_norm_f32(const float* x, const void* w, void* out, int M, int W, float eps, float offset, int dtype,
                                   void* stream) {
   JL_CHECK_ARG(M >= 1 && W >= 1, "jl_norm_f32: bad shape M=%d W=%d", M, W);
-  count_launch();
-  JL_DISPATCH_DTYPE(dtype, norm_f32_kernel<T><<<M, 256, 0, (cudaStream_t)stream>>>(x, (const T*)w, (T*)out, W, eps, offset));
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(norm_f32_kernel<T>, dim3(M), dim3(256), 0, (cudaStream_t)stream, x, (const T*)w, (T*)out, W, eps, offset));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }
@@ -204,20 +215,19 @@ extern "C" JL_API int jl_postnorm_add(const float* y, int ldy, const void* w_pos
                                       int W, float eps, float offset, int dtype, void* stream) {
   JL_CHECK_ARG(M >= 1 && W >= 1 && ldy >= W, "jl_postnorm_add: bad shape M=%d W=%d ldy=%d", M, W, ldy);
   JL_CHECK_ARG((w_next == nullptr) == (h == nullptr), "jl_postnorm_add: w_next and h come together");
-  count_launch();
   const bool vec = W % 4 == 0 && ldy % 4 == 0 && W <= 256 * 4 * 16 && (uintptr_t)y % 16 == 0 && (uintptr_t)x % 16 == 0 &&
                    (uintptr_t)w_post % 16 == 0 && (uintptr_t)w_next % 16 == 0 && (uintptr_t)h % 16 == 0;
   if (vec) {
     const int vpt = (W / 4 + 255) / 256;
 #define JL_PN(V)                                                                                                         \
-  JL_DISPATCH_DTYPE(dtype, postnorm_add_vec_kernel<T, V><<<M, 256, 0, (cudaStream_t)stream>>>(y, ldy, (const T*)w_post, x, \
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL((postnorm_add_vec_kernel<T, V>), dim3(M), dim3(256), 0, (cudaStream_t)stream, y, ldy, (const T*)w_post, x, \
                                                                                                (const T*)w_next, (T*)h, W, eps, offset))
     if (vpt <= 1) JL_PN(1); else if (vpt <= 2) JL_PN(2); else if (vpt <= 4) JL_PN(4); else if (vpt <= 8) JL_PN(8); else JL_PN(16);
 #undef JL_PN
     JL_CUDA(cudaGetLastError());
     return JL_OK;
   }
-  JL_DISPATCH_DTYPE(dtype, postnorm_add_kernel<T><<<M, 256, 0, (cudaStream_t)stream>>>(y, ldy, (const T*)w_post, x,
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(postnorm_add_kernel<T>, dim3(M), dim3(256), 0, (cudaStream_t)stream, y, ldy, (const T*)w_post, x,
                                                                                         (const T*)w_next, (T*)h, W, eps, offset));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
@@ -227,8 +237,7 @@ extern "C" JL_API int jl_headnorm_gate(const float* o, const void* w, const floa
                                        float eps, int gate_act, int dtype, void* stream) {
   JL_CHECK_ARG(M >= 1 && H >= 1 && V >= 1, "jl_headnorm_gate: bad shape M=%d H=%d V=%d", M, H, V);
   const int warps = 4, blocks = (M * H + warps - 1) / warps;
-  count_launch();
-  JL_DISPATCH_DTYPE(dtype, headnorm_gate_kernel<T><<<blocks, warps * 32, 0, (cudaStream_t)stream>>>(
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(headnorm_gate_kernel<T>, dim3(blocks), dim3(warps * 32), 0, (cudaStream_t)stream, 
                                o, (const T*)w, gate, ldg, (T*)out, M, H, V, eps, gate_act));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
@@ -239,8 +248,7 @@ extern "C" JL_API int jl_act_cast(const float* in, int ldi, void* out, int ldo, 
   JL_CHECK_ARG(M >= 1 && N >= 1 && ldi >= N && ldo >= N, "jl_act_cast: bad shape M=%d N=%d ldi=%d ldo=%d", M, N, ldi, ldo);
   const size_t total = (size_t)M * N;
   const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-  count_launch();
-  JL_DISPATCH_DTYPE(out_dtype, act_cast_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>(in, ldi, (T*)out, ldo, M, N, act, p0, p1));
+  JL_DISPATCH_DTYPE(out_dtype, JL_LAUNCH_PDL(act_cast_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, in, ldi, (T*)out, ldo, M, N, act, p0, p1));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

@@ -46,6 +46,11 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats o
   return red[32];
 }
 
+// Launch with programmatic dependent launch enabled (common.cuh launch_pdl counts the launch).  A kernel name with template
+// commas goes in parentheses.  The launch error, if any, is read by the caller with cudaGetLastError().
+#define JL_LAUNCH_PDL(kernel, grid, block, smem, stream, ...) \
+  (void)jl::launch_pdl(kernel, grid, block, (size_t)(smem), (cudaStream_t)(stream), __VA_ARGS__)
+
 #define JL_DISPATCH_DTYPE(dt, ...)                                   \
   do {                                                               \
     if ((dt) == jl::DT_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
