@@ -76,8 +76,77 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prep_kernel(PrepParams p, 
   }
 }
 
+// Latent attention, preparation: the fused down-projection row y holds the query latent (q_rank columns at q_off) and the
+// key/value latent followed by one rotated key part shared by all heads (kv_rank + rot_dim columns at kv_off).  Both latents
+// are RMS-normed with a plain weight; the key part gets the rotary embedding of the token's position on its first `rot`
+// channels.  The normed query latent goes to cq [M][q_rank]; the normed key/value latent and the rotated key part are
+// appended as ONE cache row [kv_rank | rot_dim] at slot *cache_len + s — all that this kind of layer keeps per token.
+struct LatentPrepParams {
+  const float* y; int ldy;
+  int q_off, q_rank, kv_off, kv_rank, rot_dim, rot, layout;
+  const float* cos_t; const float* sin_t; int max_pos;
+  float eps;
+  int B, S, T;
+  const int* cache_len; const int* pad_left;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) latent_prep_kernel(LatentPrepParams p, const T* __restrict__ wq, const T* __restrict__ wkv,
+                                                          T* __restrict__ cq, T* __restrict__ cache) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
+  __shared__ float red[33];
+  const int m = blockIdx.x, b = m / p.S, s = m % p.S;
+  const int slot = (p.cache_len ? *p.cache_len : 0) + s;
+  int pos = slot - (p.pad_left ? p.pad_left[b] : 0);
+  pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+  const float* yr = p.y + (size_t)m * p.ldy;
+  if (p.q_rank > 0) {
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) { const float v = yr[p.q_off + i]; ss += v * v; }
+    const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)p.q_rank + p.eps);
+    for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x)
+      cq[(size_t)m * p.q_rank + i] = from_f<T>(yr[p.q_off + i] * r * to_f(wq[i]));
+  }
+  T* row = cache + ((size_t)b * p.T + slot) * (p.kv_rank + p.rot_dim);
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) { const float v = yr[p.kv_off + i]; ss += v * v; }
+  const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)p.kv_rank + p.eps);
+  for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) row[i] = from_f<T>(yr[p.kv_off + i] * r * to_f(wkv[i]));
+  const float* src = yr + p.kv_off + p.kv_rank;
+  const float* ct = p.cos_t + (size_t)pos * (p.rot / 2);
+  const float* st = p.sin_t + (size_t)pos * (p.rot / 2);
+  for (int d = threadIdx.x; d < p.rot_dim; d += blockDim.x)
+    row[p.kv_rank + d] = from_f<T>(rotary_channel(src, d, p.rot, p.layout, ct, st));
+}
+
+// out[m, h, out_off + d] = rotary(in[m, h, in_off + d]), d < n: a slice of every head rotated at the token's position and
+// copied into another head layout (in / out head pitches in_hs / out_hs, row pitches ldi / ldo).
+template <typename T>
+__global__ void __launch_bounds__(128) rotary_slice_kernel(const T* __restrict__ in, int ldi, int in_hs, int in_off,
+                                                           T* __restrict__ out, int ldo, int out_hs, int out_off, int H, int n,
+                                                           int rot, int layout, const float* __restrict__ cos_t,
+                                                           const float* __restrict__ sin_t, int max_pos,
+                                                           const int* __restrict__ cache_len, const int* __restrict__ pad_left,
+                                                           int S) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
+  const int m = blockIdx.x, b = m / S, s = m % S;
+  int pos = (cache_len ? *cache_len : 0) + s - (pad_left ? pad_left[b] : 0);
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+  const float* ct = cos_t + (size_t)pos * (rot / 2);
+  const float* st = sin_t + (size_t)pos * (rot / 2);
+  for (int i = threadIdx.x; i < H * n; i += blockDim.x) {
+    const int h = i / n, d = i % n;
+    out[(size_t)m * ldo + (size_t)h * out_hs + out_off + d] =
+        from_f<T>(rotary_channel(in + (size_t)m * ldi + (size_t)h * in_hs + in_off, d, rot, layout, ct, st));
+  }
+}
+
 struct AttnParams {
   int B, S, H, G, D, Dv, T;
+  int ldk, ldv;                     // row pitch of the key / value cache in elements (>= D / Dv: the two may be columns of one row)
+  int window;                       // > 0: a query at slot i sees slots i - window + 1 .. i only; 0: everything before it
   float scale;
   const int* cache_len;             // slots already filled BEFORE this call's tokens (device scalar); nullptr = 0
   const int* pad_left;
@@ -89,13 +158,13 @@ constexpr int AT_MAXV = 16;         // value columns per lane: Dv <= 512
 // scores of one block of 32 keys (lane = key), then the block's contribution to the output (lane = value column)
 template <typename T>
 __device__ __forceinline__ void attn_block(const float* __restrict__ qs, const T* __restrict__ kbase, const T* __restrict__ vbase,
-                                           int j0, int lo, int hi, int D, int Dv, float scale, float& mrun, float& lrun,
-                                           float (&acc)[AT_MAXV]) {
+                                           int j0, int lo, int hi, int D, int Dv, int ldk, int ldv, float scale, float& mrun,
+                                           float& lrun, float (&acc)[AT_MAXV]) {
   const int lane = threadIdx.x & 31;
   const int j = j0 + lane;
   float sc = -INFINITY;
   if (j >= lo && j <= hi) {
-    const T* kr = kbase + (size_t)j * D;
+    const T* kr = kbase + (size_t)j * ldk;
     float d = 0.0f;
     for (int c = 0; c < D; ++c) d = fmaf(qs[c], to_f(kr[c]), d);
     sc = d * scale;
@@ -112,7 +181,7 @@ __device__ __forceinline__ void attn_block(const float* __restrict__ qs, const T
   for (int t = 0; t < jend; ++t) {
     const float pt = __shfl_sync(0xffffffffu, pj, t);
     if (pt == 0.0f) continue;
-    const T* vr = vbase + (size_t)(j0 + t) * Dv;
+    const T* vr = vbase + (size_t)(j0 + t) * ldv;
 #pragma unroll
     for (int i = 0; i < AT_MAXV; ++i) {
       const int c = lane + 32 * i;
@@ -121,19 +190,19 @@ __device__ __forceinline__ void attn_block(const float* __restrict__ qs, const T
   }
 }
 
-// Rows j0 .. j0+31 of a cache head (row length n, rows beyond jmax read as zero) into shared memory as fp32 with row
+// Rows j0 .. j0+31 of a cache head (row length n, row pitch ld, rows beyond jmax read as zero) into shared memory as fp32 with row
 // pitch `pitch`; 16-byte global loads when a row is a whole number of them, else element by element (which also zeroes
 // the columns between n and the next multiple of four, the part of the pitch the dot products read).
 template <typename T>
-__device__ __forceinline__ void stage_rows(float* dst, int pitch, const T* __restrict__ src, int n, int j0, int jmax) {
+__device__ __forceinline__ void stage_rows(float* dst, int pitch, const T* __restrict__ src, int n, int ld, int j0, int jmax) {
   constexpr int VN = 16 / sizeof(T);
-  if (n % VN == 0 && ((uintptr_t)src & 15) == 0) {
+  if (n % VN == 0 && ld % VN == 0 && ((uintptr_t)src & 15) == 0) {
     const int per_row = n / VN;
     for (int i = threadIdx.x; i < 32 * per_row; i += blockDim.x) {
       const int r = i / per_row, cv = i % per_row, j = j0 + r;
       float* d = dst + r * pitch + cv * VN;
       if (j <= jmax) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)j * n + cv * VN);
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)j * ld + cv * VN);
         if constexpr (sizeof(T) == 2) {
           *reinterpret_cast<float4*>(d) = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
           *reinterpret_cast<float4*>(d + 4) = make_float4(bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w));
@@ -150,7 +219,7 @@ __device__ __forceinline__ void stage_rows(float* dst, int pitch, const T* __res
   const int np = (n + 3) & ~3;
   for (int i = threadIdx.x; i < 32 * np; i += blockDim.x) {
     const int r = i / np, c = i % np, j = j0 + r;
-    dst[r * pitch + c] = (j <= jmax && c < n) ? to_f(src[(size_t)j * n + c]) : 0.0f;
+    dst[r * pitch + c] = (j <= jmax && c < n) ? to_f(src[(size_t)j * ld + c]) : 0.0f;
   }
 }
 
@@ -178,12 +247,13 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, 
   const int base = p.cache_len ? *p.cache_len : 0;
   const int lo = p.pad_left ? p.pad_left[b] : 0;
   const int hi_cta = base + min(q0 + AR_QB, p.S) - 1;    // last key any query of this CTA sees
+  const int lo_cta = p.window > 0 ? max(lo, base + q0 - p.window + 1) : lo;      // first key any query of this CTA sees
   for (int i = threadIdx.x; i < AR_QB * DP; i += blockDim.x) {
     const int r = i / DP, c = i % DP, s = q0 + r;
     Qs[i] = (s < p.S && c < p.D) ? to_f(q[((size_t)(b * p.S + s) * p.H + h) * p.D + c]) : 0.0f;
   }
-  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.D;
-  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.Dv;
+  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.ldk;
+  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.ldv;
   float mrun[AR_QW], lrun[AR_QW], acc[AR_QW][NV];
 #pragma unroll
   for (int qi = 0; qi < AR_QW; ++qi) {
@@ -191,19 +261,20 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, 
 #pragma unroll
     for (int i = 0; i < NV; ++i) acc[qi][i] = 0.0f;
   }
-  for (int j0 = lo & ~31; j0 <= hi_cta; j0 += 32) {
+  for (int j0 = lo_cta & ~31; j0 <= hi_cta; j0 += 32) {
     __syncthreads();                                     // the previous tile is no longer read
-    stage_rows<T>(Ks, DP, kbase, p.D, j0, hi_cta);
-    stage_rows<T>(Vs, DVP, vbase, p.Dv, j0, hi_cta);
+    stage_rows<T>(Ks, DP, kbase, p.D, p.ldk, j0, hi_cta);
+    stage_rows<T>(Vs, DVP, vbase, p.Dv, p.ldv, j0, hi_cta);
     __syncthreads();
 #pragma unroll
     for (int qi = 0; qi < AR_QW; ++qi) {
       const int s = q0 + warp * AR_QW + qi;
       const int hi = base + s;
-      if (s >= p.S || j0 > hi) continue;                 // warp-uniform
+      const int lo_q = p.window > 0 ? max(lo, hi - p.window + 1) : lo;
+      if (s >= p.S || j0 > hi || j0 + 31 < lo_q) continue;      // warp-uniform
       const int j = j0 + lane;
       float sc = -INFINITY;
-      if (j >= lo && j <= hi) {
+      if (j >= lo_q && j <= hi) {
         const float4* kr = reinterpret_cast<const float4*>(Ks + lane * DP);
         const float4* qr = reinterpret_cast<const float4*>(Qs + (warp * AR_QW + qi) * DP);
         float d0 = 0.0f, d1 = 0.0f;
@@ -265,13 +336,14 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(AttnParams p
   const T* qr = q + ((size_t)b * p.H + h) * p.D;
   for (int c = threadIdx.x; c < p.D; c += blockDim.x) qs[c] = to_f(qr[c]);
   __syncthreads();
-  const int lo = p.pad_left ? p.pad_left[b] : 0;
   const int hi = p.cache_len ? *p.cache_len : 0;
-  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.D;
-  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.Dv;
+  int lo = p.pad_left ? p.pad_left[b] : 0;
+  if (p.window > 0) lo = max(lo, hi - p.window + 1);
+  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.ldk;
+  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.ldv;
   float mrun = -INFINITY, lrun = 0.0f, acc[AT_MAXV] = {};
   for (int j0 = (lo & ~31) + 32 * warp; j0 <= hi; j0 += 32 * AD_WARPS)
-    attn_block<T>(qs, kbase, vbase, j0, lo, hi, p.D, p.Dv, p.scale, mrun, lrun, acc);
+    attn_block<T>(qs, kbase, vbase, j0, lo, hi, p.D, p.Dv, p.ldk, p.ldv, p.scale, mrun, lrun, acc);
   if (lane == 0) { ml[2 * warp] = mrun; ml[2 * warp + 1] = lrun; }
 #pragma unroll
   for (int i = 0; i < AT_MAXV; ++i) {
@@ -313,14 +385,15 @@ __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p,
   const int DVP = (p.Dv + 3) & ~3;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
-  const int lo = p.pad_left ? p.pad_left[b] : 0;
   const int hi = p.cache_len ? *p.cache_len : 0;         // the new token's own slot
+  int lo = p.pad_left ? p.pad_left[b] : 0;
+  if (p.window > 0) lo = max(lo, hi - p.window + 1);
   for (int i = threadIdx.x; i < R * DP; i += blockDim.x) {
     const int r = i / DP, c = i % DP;
     Qs[i] = c < p.D ? to_f(q[((size_t)b * p.H + g * R + r) * p.D + c]) : 0.0f;
   }
-  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.D;
-  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.Dv;
+  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.ldk;
+  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.ldv;
   float mrun[AS_RW], lrun[AS_RW], acc[AS_RW][NV];
 #pragma unroll
   for (int qi = 0; qi < AS_RW; ++qi) {
@@ -330,8 +403,8 @@ __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p,
   }
   for (int j0 = (lo & ~31) + 32 * z; j0 <= hi; j0 += 32 * splits) {
     __syncthreads();
-    stage_rows<T>(Ks, DP, kbase, p.D, j0, hi);
-    stage_rows<T>(Vs, DVP, vbase, p.Dv, j0, hi);
+    stage_rows<T>(Ks, DP, kbase, p.D, p.ldk, j0, hi);
+    stage_rows<T>(Vs, DVP, vbase, p.Dv, p.ldv, j0, hi);
     __syncthreads();
     const int j = j0 + lane;
     const bool vis = j >= lo && j <= hi;
@@ -451,12 +524,13 @@ extern "C" JL_API int jl_attn_generic_splits(int B, int H, int G, int T_cap) {
   return s < 1 ? 1 : s;
 }
 
-extern "C" JL_API int jl_attn_generic(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
-                                      const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv,
-                                      int T_cap, float scale, float* scratch, int splits, int dtype, void* stream) {
+static int attn_launch(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
+                       const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk,
+                       int ldv, int window, float scale, float* scratch, int splits, int dtype, void* stream) {
   JL_CHECK_ARG(B >= 1 && S >= 1 && G >= 1 && H % G == 0, "jl_attn_generic: H=%d not a multiple of G=%d", H, G);
   JL_CHECK_ARG(Dv <= 32 * AT_MAXV, "jl_attn_generic: value size %d above %d", Dv, 32 * AT_MAXV);
-  AttnParams p{B, S, H, G, D, Dv, T_cap, scale, cache_len, pad_left, gate, ldg};
+  JL_CHECK_ARG(ldk >= D && ldv >= Dv && window >= 0, "jl_attn_generic: bad pitch %d / %d or window %d", ldk, ldv, window);
+  AttnParams p{B, S, H, G, D, Dv, T_cap, ldk, ldv, window, scale, cache_len, pad_left, gate, ldg};
   cudaStream_t st = (cudaStream_t)stream;
   if (S == 1 && scratch != nullptr && splits >= 1 && H / G <= AS_WARPS * AS_RW) {
     const int dp = ((D + 3) & ~3) + 4;
@@ -493,6 +567,48 @@ extern "C" JL_API int jl_attn_generic(const void* q, const void* k_cache, const 
     if (nv <= 1) JL_AR(1); else if (nv <= 2) JL_AR(2); else if (nv <= 4) JL_AR(4); else if (nv <= 8) JL_AR(8); else JL_AR(16);
 #undef JL_AR
   }
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+extern "C" JL_API int jl_attn_generic(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
+                                      const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv,
+                                      int T_cap, float scale, float* scratch, int splits, int dtype, void* stream) {
+  return attn_launch(q, k_cache, v_cache, out, gate, ldg, cache_len, pad_left, B, S, H, G, D, Dv, T_cap, D, Dv, 0, scale, scratch,
+                     splits, dtype, stream);
+}
+
+extern "C" JL_API int jl_attn_windowed(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cache_len,
+                                       const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk, int ldv,
+                                       int window, float scale, float* scratch, int splits, int dtype, void* stream) {
+  return attn_launch(q, k_cache, v_cache, out, nullptr, 0, cache_len, pad_left, B, S, H, G, D, Dv, T_cap, ldk, ldv, window, scale,
+                     scratch, splits, dtype, stream);
+}
+
+extern "C" JL_API int jl_latent_prep(const float* y, int ldy, int q_off, int q_rank, int kv_off, int kv_rank, int rot_dim, int rot,
+                                     int layout, const void* wq_norm, const void* wkv_norm, void* cq, void* cache,
+                                     const float* cos_t, const float* sin_t, int max_pos, float eps, const int* cache_len,
+                                     const int* pad_left, int B, int S, int T_cap, int dtype, void* stream) {
+  JL_CHECK_ARG(B >= 1 && S >= 1 && q_rank >= 0 && kv_rank >= 1 && rot_dim >= 0, "jl_latent_prep: bad shape");
+  JL_CHECK_ARG(rot >= 0 && rot <= rot_dim && rot % 2 == 0, "jl_latent_prep: rot=%d must be even and <= rot_dim=%d", rot, rot_dim);
+  JL_CHECK_ARG(layout == 0 || layout == 1, "jl_latent_prep: layout %d", layout);
+  LatentPrepParams p{y, ldy, q_off, q_rank, kv_off, kv_rank, rot_dim, rot, layout, cos_t, sin_t, max_pos, eps, B, S, T_cap,
+                     cache_len, pad_left};
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(latent_prep_kernel<T>, dim3(B * S), dim3(128), 0, (cudaStream_t)stream, p, (const T*)wq_norm,
+                                         (const T*)wkv_norm, (T*)cq, (T*)cache));
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+extern "C" JL_API int jl_rotary_slice(const void* in, int ldi, int in_hs, int in_off, void* out, int ldo, int out_hs, int out_off,
+                                      int H, int n, int rot, int layout, const float* cos_t, const float* sin_t, int max_pos,
+                                      const int* cache_len, const int* pad_left, int B, int S, int dtype, void* stream) {
+  JL_CHECK_ARG(B >= 1 && S >= 1 && H >= 1 && n >= 1, "jl_rotary_slice: bad shape");
+  JL_CHECK_ARG(rot >= 0 && rot <= n && rot % 2 == 0 && (layout == 0 || layout == 1), "jl_rotary_slice: rot=%d of n=%d, layout %d", rot,
+               n, layout);
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(rotary_slice_kernel<T>, dim3(B * S), dim3(128), 0, (cudaStream_t)stream, (const T*)in, ldi,
+                                         in_hs, in_off, (T*)out, ldo, out_hs, out_off, H, n, rot, layout, cos_t, sin_t, max_pos,
+                                         cache_len, pad_left, S));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

@@ -23,6 +23,10 @@ constexpr int GS_TC = 8;         // tokens staged per chunk
 constexpr int GS_THREADS = 128;
 constexpr int GS_PITCH = GS_DP + 4;   // floats per 32 channels in shared memory: 16-byte aligned rows, distinct banks per lane group
 
+__device__ __forceinline__ float log_sigmoid(float z) {
+  return z >= 0.0f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
+}
+
 struct GlaParams {
   const float* y; int ldy;
   int q_off, k_off, v_off, a_off;      // columns of y: q [H*D], k [H*D], v [H*Dv], low-rank decay input [R]
@@ -35,11 +39,42 @@ struct GlaParams {
   int NC, L, mode;                     // mode 0: one chunk, state in / out; 1: local scan from zero, no read-out; 3: read-out pass
   float* cstate;                       // [B][NC][H][D][Dv]: local end states (after mode 1), incoming states (after the combine)
   float* cdecay;                       // [B][NC][H][D]: product of the chunk's decays per key channel
+  // retention (jl_retention_scan): one fixed decay per head instead of the projected one, rotary embedding of q and k at the
+  // token's position, k scaled after the rotation
+  const float* head_decay;             // [H] fp32, or nullptr: alpha from the low-rank projection
+  const float* cos_t; const float* sin_t; int rot, layout, max_pos;      // tables [max_pos][rot/2]; rot == 0: no rotation
+  float k_scale;
 };
 
-__device__ __forceinline__ float log_sigmoid(float z) {
-  return z >= 0.0f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
+// q, k and alpha of channel d of head h for the token whose projection row is yr (position pos).
+template <typename T>
+__device__ __forceinline__ void scan_channel(const GlaParams& p, const float* __restrict__ yr, int h, int d, int pos,
+                                             const float* __restrict__ zs, const T* __restrict__ a2, const T* __restrict__ a2b,
+                                             float& qv, float& kv, float& av) {
+  const float* qh = yr + p.q_off + h * p.D;
+  const float* kh = yr + p.k_off + h * p.D;
+  if (p.rot > 0) {
+    const float* ct = p.cos_t + (size_t)pos * (p.rot / 2);
+    const float* st = p.sin_t + (size_t)pos * (p.rot / 2);
+    qv = rotary_channel(qh, d, p.rot, p.layout, ct, st) * p.q_scale;
+    kv = rotary_channel(kh, d, p.rot, p.layout, ct, st) * p.k_scale;
+  } else {
+    qv = qh[d] * p.q_scale;
+    kv = kh[d] * p.k_scale;
+  }
+  if (p.head_decay) { av = p.head_decay[h]; return; }
+  const int n = h * p.D + d;
+  float z = to_f(a2b[n]);
+  for (int r = 0; r < p.R; ++r) z = fmaf(to_f(a2[(size_t)n * p.R + r]), zs[r], z);
+  av = expf(log_sigmoid(z) * p.inv_tau);
 }
+
+__device__ __forceinline__ int scan_position(const GlaParams& p, int b, int s) {
+  if (p.rot <= 0) return 0;
+  const int pos = (p.cache_len ? *p.cache_len : 0) + s - (p.pad_left ? p.pad_left[b] : 0);
+  return pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+}
+
 
 template <typename T>
 __global__ void __launch_bounds__(GS_THREADS, 3) gla_scan_kernel(GlaParams p, const T* __restrict__ a2, const T* __restrict__ a2b) {
@@ -84,15 +119,9 @@ __global__ void __launch_bounds__(GS_THREADS, 3) gla_scan_kernel(GlaParams p, co
       const int t = i / (P * GS_DP), d = i % (P * GS_DP);
       const int at = t * DS + (d / GS_DP) * GS_PITCH + d % GS_DP;
       float qv = 0.0f, kv = 0.0f, av = 1.0f;
-      if (d < p.D) {
-        const float* yr = p.y + (size_t)(b * p.S + s0 + t) * p.ldy;
-        qv = yr[p.q_off + h * p.D + d] * p.q_scale;
-        kv = yr[p.k_off + h * p.D + d];
-        const int n = h * p.D + d;
-        float z = to_f(a2b[n]);
-        for (int r = 0; r < p.R; ++r) z = fmaf(to_f(a2[(size_t)n * p.R + r]), zs[t * p.R + r], z);
-        av = expf(log_sigmoid(z) * p.inv_tau);
-      }
+      if (d < p.D)
+        scan_channel<T>(p, p.y + (size_t)(b * p.S + s0 + t) * p.ldy, h, d, scan_position(p, b, s0 + t), zs + t * p.R, a2, a2b,
+                        qv, kv, av);
       qs[at] = qv; ks[at] = kv; as[at] = av;
     }
     __syncthreads();
@@ -157,6 +186,7 @@ __global__ void __launch_bounds__(128) gla_prep_kernel(GlaParams p, const T* __r
   extern __shared__ float zs[];                                 // [R]
   const int m = blockIdx.x;
   const float* yr = p.y + (size_t)m * p.ldy;
+  const int pos = scan_position(p, m / p.S, m % p.S);
   for (int r = threadIdx.x; r < p.R; r += blockDim.x) zs[r] = yr[p.a_off + r];
   __syncthreads();
   const int P = p.P, pitch = DP + 4, RF = gla_record_floats(P, DP, p.Dv);
@@ -165,14 +195,7 @@ __global__ void __launch_bounds__(128) gla_prep_kernel(GlaParams p, const T* __r
   for (int i = threadIdx.x; i < p.H * per_head; i += blockDim.x) {
     const int h = i / per_head, d = i % per_head;
     float qv = 0.0f, kv = 0.0f, av = 1.0f;
-    if (d < p.D) {
-      qv = yr[p.q_off + h * p.D + d] * p.q_scale;
-      kv = yr[p.k_off + h * p.D + d];
-      const int n = h * p.D + d;
-      float z = to_f(a2b[n]);
-      for (int r = 0; r < p.R; ++r) z = fmaf(to_f(a2[(size_t)n * p.R + r]), zs[r], z);
-      av = expf(log_sigmoid(z) * p.inv_tau);
-    }
+    if (d < p.D) scan_channel<T>(p, yr, h, d, pos, zs, a2, a2b, qv, kv, av);
     float* o = out + (size_t)h * RF + (d / DP) * pitch + d % DP;
     o[0] = qv; o[P * pitch] = kv; o[2 * P * pitch] = av;
   }
@@ -349,17 +372,14 @@ extern "C" JL_API size_t jl_gla_scan_ws_floats(int B, int S, int H, int D, int D
   return n;
 }
 
-extern "C" JL_API int jl_gla_scan(const float* y, int ldy, int q_off, int k_off, int v_off, int a_off, const void* a2,
-                                  const void* a2_bias, float* state, float* o, const int* cache_len, const int* pad_left, int B,
-                                  int S, int H, int D, int Dv, int R, float q_scale, float tau, float* ws, int dtype,
-                                  void* stream) {
-  JL_CHECK_ARG(B >= 1 && S >= 1 && H >= 1 && D >= 1 && Dv >= 1 && R >= 1, "jl_gla_scan: bad shape");
-  JL_CHECK_ARG(tau > 0.0f, "jl_gla_scan: tau=%f must be positive", tau);
+// Both scans (projected decays; fixed decays with rotary q / k) share the kernels: what differs is in p.
+static int launch_scan(GlaParams p, const void* a2, const void* a2_bias, float* ws, int dtype, void* stream) {
+  const int B = p.B, S = p.S, H = p.H, D = p.D, Dv = p.Dv, R = p.R;
   int P = 1;
   while (P * GS_DP < D) P *= 2;
   JL_CHECK_ARG(P <= 32, "jl_gla_scan: key size %d above %d", D, 32 * GS_DP);
   const int cols = GS_THREADS / P;
-  GlaParams p{y, ldy, q_off, k_off, v_off, a_off, B, S, H, D, Dv, R, P, q_scale, 1.0f / tau, cache_len, pad_left, state, o};
+  p.P = P;
   const size_t smem = (size_t)(3 * GS_TC * P * GS_PITCH + GS_TC * cols + GS_TC * R) * sizeof(float);
   JL_CHECK_ARG(smem <= 200 * 1024, "jl_gla_scan: key size %d with rank %d does not fit the staging buffer", D, R);
   dim3 grid((Dv + cols - 1) / cols, H, B), block(GS_THREADS);
@@ -403,4 +423,28 @@ extern "C" JL_API int jl_gla_scan(const float* y, int ldy, int q_off, int k_off,
   JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(gla_scan_kernel<T>, dim3(grid), dim3(block), smem, (cudaStream_t)stream, p, (const T*)a2, (const T*)a2_bias));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
+}
+
+extern "C" JL_API int jl_gla_scan(const float* y, int ldy, int q_off, int k_off, int v_off, int a_off, const void* a2,
+                                  const void* a2_bias, float* state, float* o, const int* cache_len, const int* pad_left, int B,
+                                  int S, int H, int D, int Dv, int R, float q_scale, float tau, float* ws, int dtype,
+                                  void* stream) {
+  JL_CHECK_ARG(B >= 1 && S >= 1 && H >= 1 && D >= 1 && Dv >= 1 && R >= 1, "jl_gla_scan: bad shape");
+  JL_CHECK_ARG(tau > 0.0f, "jl_gla_scan: tau=%f must be positive", tau);
+  GlaParams p{y, ldy, q_off, k_off, v_off, a_off, B, S, H, D, Dv, R, 1, q_scale, 1.0f / tau, cache_len, pad_left, state, o};
+  p.k_scale = 1.0f;
+  return launch_scan(p, a2, a2_bias, ws, dtype, stream);
+}
+
+extern "C" JL_API int jl_retention_scan(const float* y, int ldy, int q_off, int k_off, int v_off, const float* head_decay,
+                                        const float* cos_t, const float* sin_t, int max_pos, int rot, int layout, float q_scale,
+                                        float k_scale, float* state, float* o, const int* cache_len, const int* pad_left, int B,
+                                        int S, int H, int D, int Dv, float* ws, void* stream) {
+  JL_CHECK_ARG(B >= 1 && S >= 1 && H >= 1 && D >= 1 && Dv >= 1 && head_decay != nullptr, "jl_retention_scan: bad shape");
+  JL_CHECK_ARG(rot >= 0 && rot <= D && rot % 2 == 0 && (layout == 0 || layout == 1), "jl_retention_scan: rot=%d of D=%d, layout %d",
+               rot, D, layout);
+  GlaParams p{y, ldy, q_off, k_off, v_off, 0, B, S, H, D, Dv, 0, 1, q_scale, 1.0f, cache_len, pad_left, state, o};
+  p.head_decay = head_decay; p.cos_t = cos_t; p.sin_t = sin_t; p.rot = rot; p.layout = layout; p.max_pos = max_pos;
+  p.k_scale = k_scale;
+  return launch_scan(p, nullptr, nullptr, ws, DT_F32, stream);
 }

@@ -125,7 +125,88 @@ __global__ void __launch_bounds__(256) postnorm_add_vec_kernel(const float* __re
   }
 }
 
-// One warp per (token, head): out = o / sqrt(mean_v(o^2) + eps) * w[v] * act(gate)
+// Residual step of a block whose branches read the same input: x[m, :] += mult * (y1[m, :] + y2[m, :]) (y1 / y2 may be
+// absent), then up to two norms of the updated row with plain weights: h1 = norm(x) * w1, h2 = norm(x) * w2 (the inputs of
+// the next block's two branches).  With y1 == y2 == nullptr it only forms the norms.  The row is kept in registers:
+// 4 floats per thread and step, W <= 256 * 4 * VPT on the vector path.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256) branch_add_norm_kernel(const float* __restrict__ y1, int ld1, const float* __restrict__ y2,
+                                                              int ld2, float mult, float* __restrict__ x,
+                                                              const T* __restrict__ w1, T* __restrict__ h1,
+                                                              const T* __restrict__ w2, T* __restrict__ h2, int W, float eps,
+                                                              int vec) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
+  __shared__ float red[33];
+  const size_t m = blockIdx.x;
+  float* xr = x + m * W;
+  const float* a = y1 ? y1 + m * ld1 : nullptr;
+  const float* b = y2 ? y2 + m * ld2 : nullptr;
+  float ss = 0.0f;
+  if (vec) {
+    const int nv = W / 4;
+    float xv[VPT][4];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      if (idx < nv) {
+        load4(xr + 4 * idx, xv[i]);
+        if (a || b) {
+          float s[4] = {0.f, 0.f, 0.f, 0.f}, t[4];
+          if (a) load4(a + 4 * idx, s);
+          if (b) { load4(b + 4 * idx, t);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[j] += t[j]; }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) xv[i][j] = fmaf(mult, s[j], xv[i][j]);
+          store4(xr + 4 * idx, xv[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ss += xv[i][j] * xv[i][j];
+      }
+    }
+    if (w1 == nullptr && w2 == nullptr) return;
+    const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      if (idx < nv) {
+        float wv[4], hv[4];
+        if (w1) {
+          load4(w1 + 4 * idx, wv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) hv[j] = xv[i][j] * r * wv[j];
+          store4(h1 + m * W + 4 * idx, hv);
+        }
+        if (w2) {
+          load4(w2 + 4 * idx, wv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) hv[j] = xv[i][j] * r * wv[j];
+          store4(h2 + m * W + 4 * idx, hv);
+        }
+      }
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = xr[i];
+    if (a || b) {
+      const float s = (a ? a[i] : 0.0f) + (b ? b[i] : 0.0f);
+      v = fmaf(mult, s, v);
+      xr[i] = v;
+    }
+    ss += v * v;
+  }
+  if (w1 == nullptr && w2 == nullptr) return;
+  const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {       // each thread re-reads the elements it wrote itself
+    const float v = xr[i] * r;
+    if (w1) h1[m * W + i] = from_f<T>(v * to_f(w1[i]));
+    if (w2) h2[m * W + i] = from_f<T>(v * to_f(w2[i]));
+  }
+}
+
+// One warp per (token, head): out = o / sqrt(mean_v(o^2) + eps) * w[v] * act(gate)   (w == nullptr: no weight)
 template <typename T>
 __global__ void headnorm_gate_kernel(const float* __restrict__ o, const T* __restrict__ w, const float* __restrict__ gate,
                                      int ldg, T* __restrict__ out, int M, int H, int V, float eps, int gate_act) {
@@ -140,7 +221,7 @@ __global__ void headnorm_gate_kernel(const float* __restrict__ o, const T* __res
   const float r = 1.0f / sqrtf(warp_sum(ss) / (float)V + eps);
   const float* grow = gate + (size_t)m * ldg + (size_t)hh * V;
   for (int i = lane; i < V; i += 32)
-    out[((size_t)m * H + hh) * V + i] = from_f<T>(orow[i] * r * to_f(w[i]) * apply_act(grow[i], gate_act, 0.f, 0.f));
+    out[((size_t)m * H + hh) * V + i] = from_f<T>(orow[i] * r * (w ? to_f(w[i]) : 1.0f) * apply_act(grow[i], gate_act, 0.f, 0.f));
 }
 
 // out[m, n] = act(in[m, n]) for an fp32 [M, N] block with row pitch ldi; out has pitch ldo (may alias in for OutT = float)
@@ -229,6 +310,24 @@ extern "C" JL_API int jl_postnorm_add(const float* y, int ldy, const void* w_pos
   }
   JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(postnorm_add_kernel<T>, dim3(M), dim3(256), 0, (cudaStream_t)stream, y, ldy, (const T*)w_post, x,
                                                                                         (const T*)w_next, (T*)h, W, eps, offset));
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+extern "C" JL_API int jl_branch_add_norm(const float* y1, int ld1, const float* y2, int ld2, float mult, float* x, const void* w1,
+                                         void* h1, const void* w2, void* h2, int M, int W, float eps, int dtype, void* stream) {
+  JL_CHECK_ARG(M >= 1 && W >= 1, "jl_branch_add_norm: bad shape M=%d W=%d", M, W);
+  JL_CHECK_ARG((w1 == nullptr) == (h1 == nullptr) && (w2 == nullptr) == (h2 == nullptr), "jl_branch_add_norm: a weight and its output come together");
+  JL_CHECK_ARG((y1 == nullptr || ld1 >= W) && (y2 == nullptr || ld2 >= W), "jl_branch_add_norm: row pitch below W=%d", W);
+  const bool vec = W % 4 == 0 && (y1 == nullptr || ld1 % 4 == 0) && (y2 == nullptr || ld2 % 4 == 0) && W <= 256 * 4 * 16 &&
+                   (uintptr_t)y1 % 16 == 0 && (uintptr_t)y2 % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w1 % 16 == 0 &&
+                   (uintptr_t)w2 % 16 == 0 && (uintptr_t)h1 % 16 == 0 && (uintptr_t)h2 % 16 == 0;
+  const int vpt = vec ? (W / 4 + 255) / 256 : 1;
+#define JL_BA(V)                                                                                                              \
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL((branch_add_norm_kernel<T, V>), dim3(M), dim3(256), 0, (cudaStream_t)stream, y1, ld1, y2, ld2, \
+                                         mult, x, (const T*)w1, (T*)h1, (const T*)w2, (T*)h2, W, eps, (int)vec))
+  if (vpt <= 1) JL_BA(1); else if (vpt <= 2) JL_BA(2); else if (vpt <= 4) JL_BA(4); else if (vpt <= 8) JL_BA(8); else JL_BA(16);
+#undef JL_BA
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

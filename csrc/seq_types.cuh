@@ -31,6 +31,22 @@ __device__ __forceinline__ float apply_act(float z, int act, float p0, float p1)
   }
 }
 
+// Channel d of a head after the rotary embedding of its first `rot` channels (even): the pair (u, v) turns into
+// (u cos - v sin, v cos + u sin).  layout 0 pairs channel 2i with 2i+1, layout 1 pairs channel i with i + rot/2; ct / st are
+// the cos / sin of the token's position for the rot/2 pairs (any factor on them is already in the table).
+template <typename S>
+__device__ __forceinline__ float rotary_channel(const S* __restrict__ src, int d, int rot, int layout, const float* __restrict__ ct,
+                                                const float* __restrict__ st) {
+  if (d >= rot) return to_f(src[d]);
+  if (layout == 0) {
+    const int i = d >> 1;
+    return (d & 1) ? to_f(src[d]) * ct[i] + to_f(src[d - 1]) * st[i] : to_f(src[d]) * ct[i] - to_f(src[d + 1]) * st[i];
+  }
+  const int half = rot >> 1;
+  return d < half ? to_f(src[d]) * ct[d] - to_f(src[d + half]) * st[d]
+                  : to_f(src[d]) * ct[d - half] + to_f(src[d - half]) * st[d - half];
+}
+
 __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats of shared memory */) {
   v = warp_sum(v);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;

@@ -305,6 +305,56 @@ int jl_gla_scan(const float* y, int ldy, int q_off, int k_off, int v_off, int a_
                 float* state, float* o, const int* cache_len, const int* pad_left, int B, int S, int H, int D, int Dv, int R,
                 float q_scale, float tau, float* ws, int dtype, void* stream);
 
+/* Retention scan: the scan above with one fixed decay per head (head_decay fp32 [H]) instead of the projected one, the rotary
+ * embedding of q and k at the token's position on the first `rot` channels of a head (layout 0: channel 2i with 2i+1; 1: channel
+ * i with i + rot/2; tables fp32 [max_pos][rot/2], any factor on cos / sin already in them) and k scaled by k_scale after it. */
+int jl_retention_scan(const float* y, int ldy, int q_off, int k_off, int v_off, const float* head_decay, const float* cos_t,
+                      const float* sin_t, int max_pos, int rot, int layout, float q_scale, float k_scale, float* state, float* o,
+                      const int* cache_len, const int* pad_left, int B, int S, int H, int D, int Dv, float* ws, void* stream);
+/* Residual step of a block whose branches read the same input: x[m] += mult * (y1[m] + y2[m]) (either may be NULL), then up to
+ * two norms of the new row with plain weights: h1 = norm(x) * w1, h2 = norm(x) * w2 (a weight and its output come together). */
+int jl_branch_add_norm(const float* y1, int ld1, const float* y2, int ld2, float mult, float* x, const void* w1, void* h1,
+                       const void* w2, void* h2, int M, int W, float eps, int dtype, void* stream);
+/* Many products act(x W^T) in one launch.  Plain batches (tile_group == NULL): batch z < nbatch reads x + (z / x_div) * x_bs,
+ * the weights w + (w_index ? w_index[z] : z) * w_bs and writes out + z * o_bs, M rows each.  Sorted rows (tile_group != NULL):
+ * M rows in tiles of jl_linear_tile_rows(), tile t uses the weights w + tile_group[t] * w_bs (< 0: skipped), row p reads
+ * input row row_src[p] (< 0: zero; NULL: p) and writes output row p. */
+int jl_linear_tile_rows(void);
+int jl_linear_grouped(const void* x, int ldx, long long x_bs, const void* w, long long w_bs, void* out, int ldo, long long o_bs,
+                      int nbatch, int x_div, int M, int N, int K, int act, float p0, float p1, const int* w_index,
+                      const int* tile_group, const int* row_src, int dtype, int out_f32, void* stream);
+/* jl_attn_generic with cache row pitches ldk / ldv (keys and values may be columns of one cached row) and a sliding window:
+ * window > 0: a query at slot i sees slots i - window + 1 .. i only. */
+int jl_attn_windowed(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cache_len,
+                     const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk, int ldv, int window,
+                     float scale, float* scratch, int splits, int dtype, void* stream);
+/* Latent attention, preparation.  y fp32 [B*S, ldy] holds the query latent (q_rank columns at q_off; 0: none) and the key /
+ * value latent followed by the rotated key part shared by the heads (kv_rank + rot_dim columns at kv_off).  The latents are
+ * RMS-normed with plain weights; the key part is rotated on its first `rot` channels.  cq [B*S, q_rank]; cache
+ * [B][T_cap][kv_rank + rot_dim], the token's row at slot *cache_len + s. */
+int jl_latent_prep(const float* y, int ldy, int q_off, int q_rank, int kv_off, int kv_rank, int rot_dim, int rot, int layout,
+                   const void* wq_norm, const void* wkv_norm, void* cq, void* cache, const float* cos_t, const float* sin_t,
+                   int max_pos, float eps, const int* cache_len, const int* pad_left, int B, int S, int T_cap, int dtype,
+                   void* stream);
+/* out[m, h, out_off + d] = rotary(in[m, h, in_off + d]), d < n, at the token's position: a slice of every head rotated and
+ * copied into another head layout (head pitches in_hs / out_hs, row pitches ldi / ldo). */
+int jl_rotary_slice(const void* in, int ldi, int in_hs, int in_off, void* out, int ldo, int out_hs, int out_off, int H, int n,
+                    int rot, int layout, const float* cos_t, const float* sin_t, int max_pos, const int* cache_len,
+                    const int* pad_left, int B, int S, int dtype, void* stream);
+/* Mixture-of-experts routing.  z fp32 [M, ldz]: router logits in columns 0 .. E-1.  score 0: sigmoid, 1: softmax.  groups > 1:
+ * experts form `groups` equal groups of neighbours, a group scores the sum of its group_top largest scores, and only experts
+ * of the `keep` best groups can be chosen.  idx int32 / wt fp32 [M, top]: the top largest, weights = scores (over their sum
+ * + 1e-20 when normalise) * scale. */
+int jl_moe_route(const float* z, int ldz, int M, int E, int top, int groups, int keep, int group_top, int score, int normalise,
+                 float scale, int* idx, float* wt, void* stream);
+/* Order the M * top (token, choice) pairs by expert into segments rounded up to `tile` rows (cap >= jl_moe_sorted_rows rows):
+ * pos [M * top]: row of each pair; row_src [cap]: token of each row (-1: padding); tile_group [cap / tile]: expert (-1: none). */
+int jl_moe_sorted_rows(int n, int E, int tile);
+int jl_moe_sort(const int* idx, int M, int top, int E, int tile, int cap, int* pos, int* row_src, int* tile_group, void* stream);
+/* out[m] = sum_k wt[m, k] * z[pos ? pos[m*top+k] : m*top+k] (+ (gate ? sigmoid(gate[m*ldg]) : 1) * shared[m] when shared). */
+int jl_moe_combine(const float* z, int ldz, const int* pos, const float* wt, int top, const float* shared, int lds,
+                   const float* gate, int ldg, float* out, int M, int W, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

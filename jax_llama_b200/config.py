@@ -15,8 +15,8 @@ import dataclasses
 import json
 import logging
 import os
-from dataclasses import dataclass
-from typing import Any, Dict, Optional
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
 
 logger = logging.getLogger(__name__)
 
@@ -243,10 +243,35 @@ def preset(name: str, **overrides: Any) -> LLaMAConfig:
 
 # --------------------------------------------------------------------------- hybrid decoder family
 @dataclass
+class RotaryScaling:
+    """Frequency interpolation for contexts longer than `original` positions: channels that make fewer than `slow`
+    turns over `original` positions are slowed by `factor`, channels that make more than `fast` turns are kept, with a
+    linear ramp over the channel index in between; cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass
 class RotarySpec:
-    """Interleaved-pair rotary embedding on the first `dims` channels of each head, frequencies base^(-2i/dims)."""
+    """Rotary embedding on the first `dims` channels of each head, frequencies base^(-2i/dims).  layout "interleaved"
+    pairs channel 2i with 2i+1, "half" pairs channel i with i + dims/2."""
     dims: int
     base: float
+    layout: str = "interleaved"
+    scaling: Optional[RotaryScaling] = None
+
+    @staticmethod
+    def parse(rot: Optional[Dict[str, Any]], layout: str = "interleaved") -> Optional["RotarySpec"]:
+        if not rot:
+            return None
+        sc = rot.get("scaling")
+        scaling = None
+        if sc:
+            scaling = RotaryScaling(factor=float(sc["factor"]), original=float(sc["original"]), fast=float(sc["fast"]),
+                                    slow=float(sc["slow"]))
+        return RotarySpec(int(rot["dims"]), float(rot["base"]), layout, scaling)
 
 
 @dataclass
@@ -277,10 +302,61 @@ class GlaMixerSpec:
 
 
 @dataclass
+class LatentAttentionMixerSpec:
+    """Softmax attention through low-rank latents: queries from a normed latent of size q_rank, keys and values from a
+    normed latent of size kv_rank (what the layer caches, with one rotated key part of rot_dim channels shared by the
+    heads).  A head's query / key is `dim` unrotated channels followed by `rot_dim` rotated ones; `window` > 0 limits a
+    query to the last `window` positions up to its own."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    rot: Optional[RotarySpec] = None
+    window: int = 0
+    kind: str = "latent_attention"
+
+
+@dataclass
+class RetentionMixerSpec:
+    """Linear attention with one fixed decay per head: S_t = decay_h S_(t-1) + k_t v_tᵀ, o_t = S_tᵀ q_t, no softmax and
+    no denominator; rotary q / k, k scaled by dim^(-1/2); read-out divided by its RMS per head, gated by silu."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: List[float] = field(default_factory=list)
+    rot: Optional[RotarySpec] = None
+    kind: str = "retention"
+
+
+@dataclass
 class DenseMlpSpec:
     ff: int
     act: str = "relu2"
     kind: str = "dense"
+
+
+@dataclass
+class MoeMlpSpec:
+    """Mixture of experts: `experts` feed-forward layers of inner size `ff`, `top` per token.  groups > 1: the experts
+    form equal groups of neighbours, a group scores the sum of its `group_top` largest scores and only the `keep` best
+    groups can be chosen.  Weights = chosen scores over their sum, times `scale`.  shared_ff > 0: one more expert runs
+    for every token, times a per-token sigmoid gate when shared_gate."""
+    experts: int
+    top: int
+    ff: int
+    act: str = "relu2"
+    score: str = "sigmoid"
+    groups: int = 1
+    keep: int = 1
+    group_top: int = 2
+    scale: float = 1.0
+    normalise: bool = True
+    shared_ff: int = 0
+    shared_gate: bool = True
+    kind: str = "moe"
 
 
 @dataclass
@@ -289,54 +365,53 @@ class HybridLayerSpec:
     mlp: Optional[DenseMlpSpec]
 
 
-class FoliraxConfig:
-    """Folirax: a decoder whose layers mix gated linear attention and softmax attention (rotary on part of each head,
-    unit-norm q / k, per-head output gates, layers that share another layer's keys and values), every sublayer wrapped
-    in a zero-centred RMS norm before and after, squared-ReLU feed-forward, scaled and soft-capped logits.
+class HybridConfig:
+    """What the configurations of the hybrid decoder family share: the JSON schema of the checkpoint's ``config.json``
+    (``architecture``, ``vocab``, ``width``, ``norm.eps`` and ``layers`` — a list of ``{"type", "mixer": {...},
+    "mlp": {...} | null}``), parsing of the layer list into specs, and the checkpoint I/O.  A design states
 
-    The JSON schema is the checkpoint's ``config.json``: ``architecture``, ``vocab``, ``width``, ``norm.eps``,
-    ``logit_scale``, ``logit_softcap`` and ``layers`` — a list of ``{"type", "mixer": {...}, "mlp": {...} | null}``.
-    """
+    * ``block``: "sandwich" — mixer and feed-forward one after the other, each between a norm before and a norm after,
+      x += norm(sublayer(norm(x))); "parallel" — both read norms of the same x, x += residual_mult · (mixer + ff);
+    * ``norm_offset``: what is added to a stored norm weight (1 for weights stored around zero);
+    * which mixer types and feed-forward kinds it has (`_parse_mixer`, `_parse_mlp`)."""
 
-    model_type = "folirax"
-    architecture = "Folirax"
+    model_type = "hybrid"
+    architecture = "Hybrid"
+    block = "sandwich"
+    norm_offset = 0.0
+    default_eps = 1e-6
 
     def __init__(self, vocab: int, width: int, layers: Any, norm: Optional[Dict[str, Any]] = None,
-                 logit_scale: float = 1.0, logit_softcap: Optional[float] = None, **extra: Any):
+                 logit_scale: float = 1.0, logit_softcap: Optional[float] = None, residual_mult: float = 1.0,
+                 **extra: Any):
         self.vocab_size = int(vocab)
         self.hidden_size = int(width)
-        self.rms_norm_eps = float((norm or {}).get("eps", 1e-6))
+        self.rms_norm_eps = float((norm or {}).get("eps", self.default_eps))
         self.logit_scale = float(logit_scale)
         self.logit_softcap = float(logit_softcap) if logit_softcap else 0.0
+        self.residual_mult = float(residual_mult)
         self.layer_dicts = copy.deepcopy(list(layers))
-        self.layers = [self._parse_layer(i, d) for i, d in enumerate(self.layer_dicts)]
+        self.layers = [HybridLayerSpec(mixer=self._parse_mixer(i, d), mlp=self._parse_mlp(i, d.get("mlp")))
+                       for i, d in enumerate(self.layer_dicts)]
         self.extra = {k: v for k, v in extra.items() if k != "architecture"}
         # generation defaults the front-end reads from every config
         self.pad_token_id, self.bos_token_id, self.eos_token_id = 0, -1, -1
         self.validate()
 
-    @staticmethod
-    def _parse_layer(i: int, d: Dict[str, Any]) -> HybridLayerSpec:
-        m = d["mixer"]
-        kind = d["type"]
-        if kind == "gla":
-            mixer: Any = GlaMixerSpec(heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), tau=float(m["tau"]))
-        elif kind == "attention":
-            rot = m.get("rot")
-            mixer = AttentionMixerSpec(
-                heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
-                scale=float(m["scale"]), rot=RotarySpec(int(rot["dims"]), float(rot["base"])) if rot else None,
-                kv_from=None if m.get("kv_from") is None else int(m["kv_from"]))
-        else:
-            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
-        mlp = d.get("mlp")
-        spec = None
-        if mlp is not None:
-            if mlp.get("kind", "dense") != "dense":
-                raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
-            spec = DenseMlpSpec(ff=int(mlp["ff"]), act=str(mlp.get("act", "relu2")))
-        return HybridLayerSpec(mixer=mixer, mlp=spec)
+    # ------------------------------------------------------------------ what a design defines
+    def _parse_mixer(self, i: int, d: Dict[str, Any]) -> Any:
+        raise NotImplementedError
 
+    def _parse_mlp(self, i: int, mlp: Optional[Dict[str, Any]]) -> Any:
+        raise NotImplementedError
+
+    def _validate_layer(self, i: int, l: "HybridLayerSpec") -> None:
+        pass
+
+    def _own_keys(self) -> Dict[str, Any]:
+        return {}
+
+    # ------------------------------------------------------------------ shared
     @property
     def num_hidden_layers(self) -> int:
         return len(self.layers)
@@ -345,41 +420,26 @@ class FoliraxConfig:
         if self.vocab_size <= 0 or self.hidden_size <= 0 or not self.layers:
             raise ValueError("vocab, width and layers must be non-empty")
         for i, l in enumerate(self.layers):
-            m = l.mixer
-            if m.kind == "attention":
-                if m.heads % m.kv_heads:
-                    raise ValueError(f"layer {i}: heads {m.heads} not a multiple of kv_heads {m.kv_heads}")
-                if m.rot is not None and (m.rot.dims % 2 or m.rot.dims > m.dim):
-                    raise ValueError(f"layer {i}: rot.dims {m.rot.dims} must be even and at most dim {m.dim}")
-                if m.kv_from is not None:
-                    if not 0 <= m.kv_from < i:
-                        raise ValueError(f"layer {i}: kv_from {m.kv_from} must name an earlier layer")
-                    src = self.layers[m.kv_from].mixer
-                    if src.kind != "attention" or src.kv_from is not None:
-                        raise ValueError(f"layer {i}: kv_from {m.kv_from} is not an attention layer with its own keys")
-                    if (src.kv_heads, src.dim, src.vdim) != (m.kv_heads, m.dim, m.vdim):
-                        raise ValueError(f"layer {i}: key / value sizes differ from layer {m.kv_from}")
-            elif m.tau <= 0:
-                raise ValueError(f"layer {i}: tau must be positive")
+            self._validate_layer(i, l)
 
     def to_dict(self) -> Dict[str, Any]:
         d: Dict[str, Any] = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
-                             "norm": {"eps": self.rms_norm_eps}, "logit_scale": self.logit_scale,
-                             "logit_softcap": self.logit_softcap, "layers": copy.deepcopy(self.layer_dicts)}
+                             "norm": {"eps": self.rms_norm_eps}, "layers": copy.deepcopy(self.layer_dicts)}
+        d.update(self._own_keys())
         d.update(self.extra)
         return d
 
     @classmethod
-    def from_dict(cls, d: Dict[str, Any]) -> "FoliraxConfig":
+    def from_dict(cls, d: Dict[str, Any]) -> "HybridConfig":
         return cls(**d)
 
     @classmethod
-    def from_json_file(cls, path: str) -> "FoliraxConfig":
+    def from_json_file(cls, path: str) -> "HybridConfig":
         with open(path) as f:
             return cls.from_dict(json.load(f))
 
     @classmethod
-    def from_pretrained(cls, path: str) -> "FoliraxConfig":
+    def from_pretrained(cls, path: str) -> "HybridConfig":
         return cls.from_json_file(os.path.join(path, CONFIG_NAME) if os.path.isdir(path) else path)
 
     def save_pretrained(self, save_directory: str) -> None:
@@ -388,4 +448,122 @@ class FoliraxConfig:
             json.dump(self.to_dict(), f, indent=1, sort_keys=True)
 
     def __repr__(self) -> str:
-        return f"FoliraxConfig {json.dumps(self.to_dict(), sort_keys=True)}"
+        return f"{type(self).__name__} {json.dumps(self.to_dict(), sort_keys=True)}"
+
+
+class FoliraxConfig(HybridConfig):
+    """Folirax: a decoder whose layers mix gated linear attention and softmax attention (rotary on part of each head,
+    unit-norm q / k, per-head output gates, layers that share another layer's keys and values), every sublayer wrapped
+    in a zero-centred RMS norm before and after, squared-ReLU feed-forward, scaled and soft-capped logits.
+
+    Besides the shared keys its ``config.json`` has ``logit_scale`` and ``logit_softcap``.
+    """
+
+    model_type = "folirax"
+    architecture = "Folirax"
+    block = "sandwich"
+    norm_offset = 1.0
+
+    def _parse_mixer(self, i: int, d: Dict[str, Any]) -> Any:
+        m = d["mixer"]
+        kind = d["type"]
+        if kind == "gla":
+            return GlaMixerSpec(heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), tau=float(m["tau"]))
+        if kind == "attention":
+            return AttentionMixerSpec(
+                heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                scale=float(m["scale"]), rot=RotarySpec.parse(m.get("rot")),
+                kv_from=None if m.get("kv_from") is None else int(m["kv_from"]))
+        raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+
+    def _parse_mlp(self, i: int, mlp: Optional[Dict[str, Any]]) -> Any:
+        if mlp is None:
+            return None
+        if mlp.get("kind", "dense") != "dense":
+            raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+        return DenseMlpSpec(ff=int(mlp["ff"]), act=str(mlp.get("act", "relu2")))
+
+    def _validate_layer(self, i: int, l: HybridLayerSpec) -> None:
+        m = l.mixer
+        if m.kind == "attention":
+            if m.heads % m.kv_heads:
+                raise ValueError(f"layer {i}: heads {m.heads} not a multiple of kv_heads {m.kv_heads}")
+            if m.rot is not None and (m.rot.dims % 2 or m.rot.dims > m.dim):
+                raise ValueError(f"layer {i}: rot.dims {m.rot.dims} must be even and at most dim {m.dim}")
+            if m.kv_from is not None:
+                if not 0 <= m.kv_from < i:
+                    raise ValueError(f"layer {i}: kv_from {m.kv_from} must name an earlier layer")
+                src = self.layers[m.kv_from].mixer
+                if src.kind != "attention" or src.kv_from is not None:
+                    raise ValueError(f"layer {i}: kv_from {m.kv_from} is not an attention layer with its own keys")
+                if (src.kv_heads, src.dim, src.vdim) != (m.kv_heads, m.dim, m.vdim):
+                    raise ValueError(f"layer {i}: key / value sizes differ from layer {m.kv_from}")
+        elif m.tau <= 0:
+            raise ValueError(f"layer {i}: tau must be positive")
+
+    def _own_keys(self) -> Dict[str, Any]:
+        return {"logit_scale": self.logit_scale, "logit_softcap": self.logit_softcap}
+
+
+class NikonexConfig(HybridConfig):
+    """Nikonex: a decoder of parallel blocks — mixer and feed-forward read two norms of the same residual stream and
+    their sum, times ``residual_mult``, is added to it.  Mixers: attention through low-rank latents with a shared
+    rotated key part, frequency-interpolated rotary embedding and a sliding window ("latent_attention"), and linear
+    attention with a fixed decay per head ("retention").  Feed-forward: a mixture of squared-ReLU experts with sigmoid
+    scores, group-limited choice and a gated shared expert.  Plain norm weights, plain logits."""
+
+    model_type = "nikonex"
+    architecture = "Nikonex"
+    block = "parallel"
+    norm_offset = 0.0
+
+    def _parse_mixer(self, i: int, d: Dict[str, Any]) -> Any:
+        m = d["mixer"]
+        kind = d["type"]
+        if kind == "latent_attention":
+            return LatentAttentionMixerSpec(
+                heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]), vdim=int(m["vdim"]),
+                q_rank=int(m["q_rank"]), kv_rank=int(m["kv_rank"]), scale=float(m["scale"]),
+                rot=RotarySpec.parse(m.get("rot"), "interleaved"), window=int((m.get("mask") or {}).get("size") or 0))
+        if kind == "retention":
+            return RetentionMixerSpec(heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                                      decay=[float(a) for a in m["decay"]], rot=RotarySpec.parse(m.get("rot"), "half"))
+        raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+
+    def _parse_mlp(self, i: int, mlp: Optional[Dict[str, Any]]) -> Any:
+        if mlp is None:
+            return None
+        if mlp.get("kind", "moe") != "moe":
+            raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+        r = mlp["router"]
+        g = r.get("groups") or {}
+        shared = mlp.get("shared") or {}
+        return MoeMlpSpec(experts=int(r["experts"]), top=int(r["top"]), ff=int(mlp["expert"]["ff"]), act="relu2",
+                          score="sigmoid", groups=int(g.get("count", 1)), keep=int(g.get("keep", g.get("count", 1))),
+                          group_top=2, scale=float(r.get("scale", 1.0)), normalise=True,
+                          shared_ff=int(shared.get("ff", 0)), shared_gate=True)
+
+    def _validate_layer(self, i: int, l: HybridLayerSpec) -> None:
+        m = l.mixer
+        if m.kind == "latent_attention":
+            if m.rot is not None and (m.rot.dims % 2 or m.rot.dims > m.rot_dim):
+                raise ValueError(f"layer {i}: rot.dims {m.rot.dims} must be even and at most rot_dim {m.rot_dim}")
+            if m.rot_dim > 0 and m.rot is None:
+                raise ValueError(f"layer {i}: rot_dim {m.rot_dim} without rot")
+            if min(m.heads, m.dim + m.rot_dim, m.vdim, m.q_rank, m.kv_rank) <= 0 or m.window < 0:
+                raise ValueError(f"layer {i}: sizes must be positive")
+        else:
+            if len(m.decay) != m.heads:
+                raise ValueError(f"layer {i}: {len(m.decay)} decays for {m.heads} heads")
+            if m.rot is not None and (m.rot.dims % 2 or m.rot.dims > m.dim):
+                raise ValueError(f"layer {i}: rot.dims {m.rot.dims} must be even and at most dim {m.dim}")
+        f = l.mlp
+        if f is not None:
+            if not 1 <= f.top <= f.experts:
+                raise ValueError(f"layer {i}: top {f.top} of {f.experts} experts")
+            if f.groups > 1 and (f.experts % f.groups or not 1 <= f.keep <= f.groups
+                                 or f.keep * (f.experts // f.groups) < f.top):
+                raise ValueError(f"layer {i}: {f.groups} groups (keep {f.keep}) cannot give {f.top} of {f.experts} experts")
+
+    def _own_keys(self) -> Dict[str, Any]:
+        return {"residual_mult": self.residual_mult}

@@ -1,0 +1,119 @@
+"""Feed-forward sublayers of the hybrid decoder family, each a small class over the kernels of `ops/seq_kernels.py`.
+
+A feed-forward owns its weights in kernel layout and turns the normalised input ``h [M, width]`` into an fp32
+``[M, width]`` branch output; norms and the residual sum belong to the layer stack (`models/hybrid_engine.py`).
+Constants (activation, score function, group limits, weight scale, shared expert) are parameters of the spec
+(`config.py`).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..config import DenseMlpSpec, MoeMlpSpec
+from ..ops import seq_kernels as SK
+from .mixers import _stack_rows
+
+
+class DenseFeedForward:
+    """down(act(up h))."""
+
+    kind = "dense"
+
+    def __init__(self, spec: DenseMlpSpec, w: Dict[str, torch.Tensor]):
+        if spec.act not in SK.ACTIVATIONS:
+            raise ValueError(f"unknown activation {spec.act!r}")
+        self.spec, self.act = spec, SK.ACTIVATIONS[spec.act]
+        self.up, self.down = w["up"].contiguous(), w["down"].contiguous()
+
+    @staticmethod
+    def shapes(spec: DenseMlpSpec, W: int) -> Dict[str, Tuple[int, ...]]:
+        return {"up": (spec.ff, W), "down": (W, spec.ff)}
+
+    def weights(self) -> List[torch.Tensor]:
+        return [self.up, self.down]
+
+    def streamed_weights(self, rows: int) -> List[torch.Tensor]:
+        return self.weights()
+
+    def run(self, h: torch.Tensor) -> torch.Tensor:
+        t = SK.linear(h, self.up, act=self.act, out_f32=False)
+        return SK.linear(t, self.down)
+
+
+class MoeFeedForward:
+    """Mixture of experts.  The router (and the shared expert's gate) is one fp32-accumulated product; a warp per
+    token chooses the experts.  Few rows (decoding): every (token, choice) pair streams its expert's two matrices in
+    one batched launch each.  Many rows (prompts): the pairs are ordered by expert into whole row tiles and each tile
+    runs against its expert's matrices.  The weighted sum, the shared expert and its gate meet in one combine pass."""
+
+    kind = "moe"
+
+    def __init__(self, spec: MoeMlpSpec, w: Dict[str, torch.Tensor]):
+        if spec.act not in SK.ACTIVATIONS or spec.score not in SK.SCORES:
+            raise ValueError(f"unknown activation {spec.act!r} or score function {spec.score!r}")
+        self.spec, self.act, self.score = spec, SK.ACTIVATIONS[spec.act], SK.SCORES[spec.score]
+        E = spec.experts
+        self.up = torch.stack([w[f"e{e}.up"] for e in range(E)]).contiguous()          # [E, ff, W]
+        self.down = torch.stack([w[f"e{e}.down"] for e in range(E)]).contiguous()      # [E, W, ff]
+        self.has_shared = spec.shared_ff > 0
+        gated = self.has_shared and spec.shared_gate
+        self.w_route, offs = _stack_rows([w["router"]] + ([w["shared.sg"]] if gated else []))
+        self.gate_off = offs[1] if gated else -1
+        self.shared_up = w["shared.up"].contiguous() if self.has_shared else None
+        self.shared_down = w["shared.down"].contiguous() if self.has_shared else None
+
+    @staticmethod
+    def shapes(spec: MoeMlpSpec, W: int) -> Dict[str, Tuple[int, ...]]:
+        out: Dict[str, Tuple[int, ...]] = {"router": (spec.experts, W)}
+        for e in range(spec.experts):
+            out[f"e{e}.up"], out[f"e{e}.down"] = (spec.ff, W), (W, spec.ff)
+        if spec.shared_ff > 0:
+            out["shared.up"], out["shared.down"] = (spec.shared_ff, W), (W, spec.shared_ff)
+            if spec.shared_gate:
+                out["shared.sg"] = (1, W)
+        return out
+
+    def weights(self) -> List[torch.Tensor]:
+        return [t for t in (self.up, self.down, self.w_route, self.shared_up, self.shared_down) if t is not None]
+
+    def streamed_weights(self, rows: int) -> List[torch.Tensor]:
+        """What a step of `rows` tokens reads at least: at most rows · top experts are touched."""
+        s = self.spec
+        frac = min(1.0, rows * s.top / s.experts)
+        n = max(1, int(round(frac * s.experts)))
+        return [self.up[:n], self.down[:n]] + [t for t in (self.w_route, self.shared_up, self.shared_down) if t is not None]
+
+    def run(self, h: torch.Tensor) -> torch.Tensor:
+        s = self.spec
+        M, W = h.shape
+        z = SK.linear(h, self.w_route)                                             # fp32 [M, router logits | gate logit]
+        idx, wt = SK.moe_route(z, s.experts, s.top, s.groups, s.keep, s.group_top, self.score, s.normalise, s.scale)
+        if M <= SK.MOE_PAIR_ROWS:
+            n = M * s.top
+            flat = idx.view(-1)
+            t = torch.empty((n, s.ff), dtype=h.dtype, device=h.device)
+            SK.linear_batched(h, self.up, t, nbatch=n, rows=1, x_bs=h.stride(0), o_bs=s.ff, x_div=s.top, w_index=flat,
+                              act=self.act)
+            y = torch.empty((n, W), dtype=torch.float32, device=h.device)
+            SK.linear_batched(t, self.down, y, nbatch=n, rows=1, x_bs=s.ff, o_bs=W, w_index=flat)
+            pos = None
+        else:
+            pos, row_src, tile_group = SK.moe_sort(idx, s.experts)
+            rows = row_src.shape[0]
+            t = torch.empty((rows, s.ff), dtype=h.dtype, device=h.device)
+            SK.linear_sorted(h, self.up, t, tile_group, row_src, act=self.act)
+            y = torch.empty((rows, W), dtype=torch.float32, device=h.device)
+            SK.linear_sorted(t, self.down, y, tile_group, None)
+        shared: Optional[torch.Tensor] = None
+        gate = None
+        if self.has_shared:
+            u = SK.linear(h, self.shared_up, act=self.act, out_f32=False)
+            shared = SK.linear(u, self.shared_down)
+            if self.gate_off >= 0:
+                gate = z[:, self.gate_off:self.gate_off + 1]
+        return SK.moe_combine(y, pos, wt, shared, gate, W)
+
+
+FEED_FORWARDS = {"dense": DenseFeedForward, "moe": MoeFeedForward}

@@ -5,7 +5,10 @@ It is the B200 engine (`models/engine.py`) with another layer stack: the request
 the decode state, on-device selection and bookkeeping, CUDA-graph replay of the decode step, `generate` and the
 token-at-a-time stream are inherited; what changes is
 
-* the weights (per-layer mixers from `models/mixers.py`, dense feed-forward, zero-centred norm weights),
+* the weights (per-layer mixers from `models/mixers.py`, feed-forwards from `models/feedforward.py`; norm weights
+  stored around zero or plain, as the configuration says),
+* the block form: sublayers one after the other, each between two norms ("sandwich"), or mixer and feed-forward
+  side by side on two norms of the same stream, their scaled sum added to it ("parallel"),
 * the cache: per attention layer a key / value cache with that layer's head sizes (none for a layer that reads another
   layer's), per recurrent layer an fp32 state, all advanced by the same device-side fill level and left-pad counts,
 * the numerics: norms, softmax, recurrences and the residual sum in fp32; matrix operands in bfloat16, or everything in
@@ -22,6 +25,7 @@ from ..ops import _lib
 from ..ops import kernels as K
 from ..ops import seq_kernels as SK
 from .engine import B200Engine, DecodeState, DeviceKVCache
+from .feedforward import FEED_FORWARDS
 from .mixers import MIXERS, rotary_table
 
 
@@ -54,27 +58,38 @@ class HybridCache(DeviceKVCache):
 class HybridLayer:
     mixer: Any
     norm1: torch.Tensor
-    norm1b: torch.Tensor
+    norm1b: Optional[torch.Tensor] = None          # norms after the sublayers: sandwich blocks only
     norm2: Optional[torch.Tensor] = None
     norm2b: Optional[torch.Tensor] = None
-    up: Optional[torch.Tensor] = None
-    down: Optional[torch.Tensor] = None
-    act: int = SK.ACT_RELU2
+    ff: Any = None
 
 
 def tensor_shapes(config: Any, decay_rank: int = 16) -> Dict[str, Tuple[int, ...]]:
     """Checkpoint tensor names → shapes for a config of this family (what a loader expects, what random_init draws).
     The rank of the decay projection is not a config key: a checkpoint fixes it by the shape of ``mix.a1``."""
     W = config.hidden_size
+    sandwich = config.block == "sandwich"
     out: Dict[str, Tuple[int, ...]] = {"embed": (config.vocab_size, W), "final.norm": (W,), "head": (config.vocab_size, W)}
     for i, l in enumerate(config.layers):
         p, m = f"l{i}.", l.mixer
-        out[p + "norm1"], out[p + "norm1b"] = (W,), (W,)
+        out[p + "norm1"] = (W,)
+        if sandwich:
+            out[p + "norm1b"] = (W,)
         if m.kind == "gla":
             out.update({p + "mix.q": (m.heads * m.dim, W), p + "mix.k": (m.heads * m.dim, W),
                         p + "mix.v": (m.heads * m.vdim, W), p + "mix.g": (m.heads * m.vdim, W),
                         p + "mix.o": (W, m.heads * m.vdim), p + "mix.norm": (m.vdim,), p + "mix.a1": (decay_rank, W),
                         p + "mix.a2": (m.heads * m.dim, decay_rank), p + "mix.a2.b": (m.heads * m.dim,)})
+        elif m.kind == "retention":
+            out.update({p + "mix.q": (m.heads * m.dim, W), p + "mix.k": (m.heads * m.dim, W),
+                        p + "mix.v": (m.heads * m.vdim, W), p + "mix.g": (m.heads * m.vdim, W),
+                        p + "mix.o": (W, m.heads * m.vdim)})
+        elif m.kind == "latent_attention":
+            out.update({p + "mix.dq": (m.q_rank, W), p + "mix.dq.norm": (m.q_rank,),
+                        p + "mix.uq": (m.heads * (m.dim + m.rot_dim), m.q_rank),
+                        p + "mix.dkv": (m.kv_rank + m.rot_dim, W), p + "mix.dkv.norm": (m.kv_rank,),
+                        p + "mix.uk": (m.heads * m.dim, m.kv_rank), p + "mix.uv": (m.heads * m.vdim, m.kv_rank),
+                        p + "mix.o": (W, m.heads * m.vdim)})
         else:
             out[p + "mix.q"] = (m.heads * m.dim, W)
             if m.kv_from is None:
@@ -83,12 +98,15 @@ def tensor_shapes(config: Any, decay_rank: int = 16) -> Dict[str, Tuple[int, ...
                 out[p + "mix.g"] = (m.heads, W)
             out[p + "mix.o"] = (W, m.heads * m.vdim)
         if l.mlp is not None:
-            out.update({p + "norm2": (W,), p + "norm2b": (W,), p + "mlp.up": (l.mlp.ff, W), p + "mlp.down": (W, l.mlp.ff)})
+            out[p + "norm2"] = (W,)
+            if sandwich:
+                out[p + "norm2b"] = (W,)
+            for name, shape in FEED_FORWARDS[l.mlp.kind].shapes(l.mlp, W).items():
+                out[p + "mlp." + name] = shape
     return out
 
 
 class HybridEngine(B200Engine):
-    norm_offset = 1.0          # norm weights are stored around zero
 
     def __init__(self, config: Any, tensors: Dict[str, torch.Tensor], *, dtype: torch.dtype = torch.bfloat16,
                  device: Any = "cuda", use_cuda_graph: bool = True):
@@ -108,6 +126,12 @@ class HybridEngine(B200Engine):
         self.mega_write_logits = False
         self.mega_max_batch = 0
         self.eps = float(config.rms_norm_eps)
+        self.norm_offset = float(config.norm_offset)          # 1: norm weights are stored around zero
+        if config.block not in ("sandwich", "parallel"):
+            raise ValueError(f"unknown block form {config.block!r}")
+        self.parallel = config.block == "parallel"
+        if self.parallel and self.norm_offset != 0.0:
+            raise ValueError("parallel blocks take plain norm weights")
         want = None
         for name, t in tensors.items():
             if name.endswith("mix.a1"):
@@ -132,15 +156,20 @@ class HybridEngine(B200Engine):
         for i, l in enumerate(config.layers):
             p = f"l{i}."
             w = {k[len(p) + 4:]: get(k) for k in want if k.startswith(p + "mix.")}
-            layer = HybridLayer(mixer=MIXERS[l.mixer.kind](l.mixer, w, self.eps), norm1=get(p + "norm1"),
-                                norm1b=get(p + "norm1b"))
+            layer = HybridLayer(mixer=MIXERS[l.mixer.kind](l.mixer, w, self.eps), norm1=get(p + "norm1"))
+            if not self.parallel:
+                layer.norm1b = get(p + "norm1b")
             if l.mlp is not None:
-                if l.mlp.act not in SK.ACTIVATIONS:
-                    raise ValueError(f"layer {i}: unknown activation {l.mlp.act!r}")
-                layer.norm2, layer.norm2b = get(p + "norm2"), get(p + "norm2b")
-                layer.up, layer.down, layer.act = get(p + "mlp.up"), get(p + "mlp.down"), SK.ACTIVATIONS[l.mlp.act]
+                layer.norm2 = get(p + "norm2")
+                if not self.parallel:
+                    layer.norm2b = get(p + "norm2b")
+                fw = {k[len(p) + 4:]: get(k) for k in want if k.startswith(p + "mlp.")}
+                try:
+                    layer.ff = FEED_FORWARDS[l.mlp.kind](l.mlp, fw)
+                except ValueError as e:
+                    raise ValueError(f"layer {i}: {e}") from None
             self.layers.append(layer)
-        self._rope: Dict[Tuple[int, float], Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._rope: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._decode_states: Dict[Tuple[int, int], DecodeState] = {}
         self._mega_gen = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._mega_fit_cache: Dict[int, bool] = {}
@@ -158,27 +187,36 @@ class HybridEngine(B200Engine):
     def _mega_fits(self, batch: int) -> bool:
         return False
 
-    def weight_bytes_per_step(self) -> int:
+    def weight_bytes_per_step(self, rows: int = 1) -> int:
+        """Bytes of weights a decode step of `rows` tokens streams (a mixture of experts: the experts it can touch)."""
         ws = [self.lm_head, self.final_norm]
         for l in self.layers:
-            ws += l.mixer.weights() + [t for t in (l.norm1, l.norm1b, l.norm2, l.norm2b, l.up, l.down) if t is not None]
+            ws += l.mixer.weights() + [t for t in (l.norm1, l.norm1b, l.norm2, l.norm2b) if t is not None]
+            if l.ff is not None:
+                ws += l.ff.streamed_weights(rows)
         return sum(t.numel() * t.element_size() for t in ws)
 
     # ------------------------------------------------------------------ rotary tables
-    def _rope_for(self, dims: int, base: float, length: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        key = (int(dims), float(base))
+    def _rope_for(self, rot: Any, length: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """cos / sin tables of a rotary spec (None: a one-row table that nothing reads), at least `length` positions."""
+        if rot is None:
+            key: Tuple = (2, 1.0, None)
+        else:
+            sc = rot.scaling
+            key = (int(rot.dims), float(rot.base), None if sc is None else (sc.factor, sc.original, sc.fast, sc.slow))
         have = self._rope.get(key)
         if have is None or have[0].shape[0] < length:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("rotary table too short for a captured step: size it before the capture")
-            self._rope[key] = have = rotary_table(dims, base, max(length, 256), self.device)
+            self._rope[key] = have = rotary_table(key[0], key[1], max(length, 256) if rot is not None else 1, self.device,
+                                                  rot.scaling if rot is not None else None)
         return have
 
     def _check_max_length(self, max_length: int) -> None:
         for l in self.layers:
-            s = l.mixer.spec
-            if l.mixer.kind == "attention" and s.rot is not None:
-                self._rope_for(s.rot.dims, s.rot.base, max_length)
+            rot = getattr(l.mixer.spec, "rot", None)
+            if rot is not None:
+                self._rope_for(rot, max_length)
 
     # ------------------------------------------------------------------ cache
     def new_cache(self, batch: int, max_length: int) -> HybridCache:
@@ -205,6 +243,8 @@ class HybridEngine(B200Engine):
     def _head(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         c = self.config
         h = SK.norm_f32(x, self.final_norm, self.eps, self.norm_offset)
+        if c.logit_scale == 1.0 and c.logit_softcap == 0.0:
+            return SK.linear(h, self.lm_head, out=out)
         return SK.linear(h, self.lm_head, act=SK.ACT_SCALE_SOFTCAP, p0=c.logit_scale, p1=c.logit_softcap, out=out)
 
     def _layers(self, x: torch.Tensor, B: int, S: int, cache: HybridCache, positions: Optional[torch.Tensor],
@@ -213,24 +253,40 @@ class HybridEngine(B200Engine):
         the recurrent states by the S tokens (padding tokens excluded); does not advance the fill level."""
         if positions is not None:
             raise NotImplementedError("explicit position_ids are not supported by the hybrid engine (left padding is)")
+        if self.parallel:
+            return self._layers_parallel(x, B, S, cache)
         eps, off = self.eps, self.norm_offset
         n = len(self.layers)
         h = SK.norm_f32(x, self.layers[0].norm1, eps, off)
         for i, l in enumerate(self.layers):
-            rope = None
-            sp = l.mixer.spec
-            if l.mixer.kind == "attention":
-                rope = self._rope_for(sp.rot.dims, sp.rot.base, cache.capacity) if sp.rot is not None else \
-                    self._rope_for(2, 1.0, 1)
+            rope = self._rope_for(getattr(l.mixer.spec, "rot", None), cache.capacity)
             u = l.mixer.run(h, B, S, cache, i, rope)
             z = SK.linear(u, l.mixer.wo)
-            nxt = l.norm2 if l.up is not None else (self.layers[i + 1].norm1 if i + 1 < n else None)
+            nxt = l.norm2 if l.ff is not None else (self.layers[i + 1].norm1 if i + 1 < n else None)
             h = SK.postnorm_add(z, l.norm1b, x, eps, off, w_next=nxt)
-            if l.up is not None:
-                t = SK.linear(h, l.up, act=l.act, out_f32=False)
-                z = SK.linear(t, l.down)
+            if l.ff is not None:
+                z = l.ff.run(h)
                 nxt = self.layers[i + 1].norm1 if i + 1 < n else None
                 h = SK.postnorm_add(z, l.norm2b, x, eps, off, w_next=nxt)
+            if self.capture_streams is not None:
+                self.capture_streams.append(x.clone())
+        return x
+
+    def _layers_parallel(self, x: torch.Tensor, B: int, S: int, cache: HybridCache) -> torch.Tensor:
+        """Parallel blocks: x += m · (mixer(norm1 x) + ff(norm2 x)).  One kernel per layer adds both branches to the
+        stream and forms the two norms the next layer reads."""
+        eps, mult = self.eps, float(self.config.residual_mult)
+        n = len(self.layers)
+        first = self.layers[0]
+        h1, h2 = SK.branch_add_norm(x, None, None, mult, first.norm1, first.norm2 if first.ff is not None else None, eps)
+        for i, l in enumerate(self.layers):
+            rope = self._rope_for(getattr(l.mixer.spec, "rot", None), cache.capacity)
+            u = l.mixer.run(h1, B, S, cache, i, rope)
+            y1 = SK.linear(u, l.mixer.wo)
+            y2 = l.ff.run(h2) if l.ff is not None else None
+            nxt = self.layers[i + 1] if i + 1 < n else None
+            h1, h2 = SK.branch_add_norm(x, y1, y2, mult, nxt.norm1 if nxt is not None else None,
+                                        nxt.norm2 if nxt is not None and nxt.ff is not None else None, eps)
             if self.capture_streams is not None:
                 self.capture_streams.append(x.clone())
         return x
@@ -266,7 +322,7 @@ def random_tensors(config: Any, device: Any = "cuda", seed: int = 0, decay_rank:
         return torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
 
     for name, shape in tensor_shapes(config, decay_rank).items():
-        if name.endswith("mix.norm"):
+        if name.endswith("mix.norm") or (config.norm_offset == 0.0 and len(shape) == 1 and "norm" in name):
             t = 1.0 + 0.1 * randn(shape)
         elif name.endswith("mix.a2.b"):
             t = 2.0 + 2.0 * randn(shape)

@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..config import AttentionMixerSpec, GlaMixerSpec
+from ..config import AttentionMixerSpec, GlaMixerSpec, LatentAttentionMixerSpec, RetentionMixerSpec, RotaryScaling
 from ..ops import _lib
 from ..ops import kernels as K
 from ..ops import seq_kernels as SK
@@ -35,12 +35,32 @@ def _stack_rows(parts: List[torch.Tensor], multiple: int = 8) -> Tuple[torch.Ten
     return torch.cat(parts, 0).contiguous(), offs
 
 
-def rotary_table(dims: int, base: float, length: int, device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
-    """cos / sin of position · base^(-2i/dims), i < dims/2, as fp32 [length, dims/2] (angles formed in float64)."""
+def rotary_frequencies(dims: int, base: float, scaling: Optional[RotaryScaling] = None) -> Tuple[torch.Tensor, float]:
+    """float64 frequencies base^(-2i/dims), i < dims/2, and the factor on cos / sin.  With `scaling`: the channel index
+    at which `original` positions make t turns is n(t) = dims · ln(original / (2π t)) / (2 ln base); channels below
+    floor(n(fast)) keep their frequency, channels above ceil(n(slow)) are divided by `factor`, linear ramp between."""
     i = torch.arange(dims // 2, dtype=torch.float64)
     freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+    if scaling is None:
+        return freq, 1.0
+
+    def channel_of(turns: float) -> float:
+        return dims * math.log(scaling.original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(channel_of(scaling.fast)), 0)
+    hi = min(math.ceil(channel_of(scaling.slow)), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return freq / scaling.factor * ramp + freq * (1.0 - ramp), 0.1 * math.log(scaling.factor) + 1.0
+
+
+def rotary_table(dims: int, base: float, length: int, device: torch.device, scaling: Optional[RotaryScaling] = None
+                 ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin of position · frequency for the dims/2 channel pairs, as fp32 [length, dims/2] (angles formed in
+    float64; the scaling's factor on cos / sin is in the table)."""
+    freq, mult = rotary_frequencies(dims, base, scaling)
     ang = torch.arange(length, dtype=torch.float64)[:, None] * freq[None, :]
-    return torch.cos(ang).float().to(device).contiguous(), torch.sin(ang).float().to(device).contiguous()
+    return ((torch.cos(ang) * mult).float().to(device).contiguous(),
+            (torch.sin(ang) * mult).float().to(device).contiguous())
 
 
 class AttentionMixer:
@@ -159,4 +179,99 @@ class GlaMixer:
         return SK.headnorm_gate(o, self.norm, gate, s.heads, s.vdim, self.eps, SK.ACT_SILU)
 
 
-MIXERS = {"attention": AttentionMixer, "gla": GlaMixer}
+class LatentAttentionMixer:
+    """Softmax attention through low-rank latents.  Per token the layer keeps one row [normed key/value latent | rotated
+    key part shared by the heads]; nothing per head.  The keys' and values' up-projections are applied on the query
+    side: with q_h = [a_h | r_h] (unrotated | rotated) the score a_h · (U_h c) + r_h · k_rot equals (U_hᵀ a_h) · c +
+    r_h · k_rot, and Σ p_j (V_h c_j) = V_h (Σ p_j c_j) — so the attention itself runs over the cached rows with one
+    shared key/value head of width kv_rank + rot_dim (keys) and kv_rank (values), in the windowed generic kernel, and
+    two per-head batched products map into and out of the latent."""
+
+    kind = "latent_attention"
+
+    def __init__(self, spec: LatentAttentionMixerSpec, w: Dict[str, torch.Tensor], eps: float):
+        self.spec, self.eps = spec, float(eps)
+        s = spec
+        self.w_in, offs = _stack_rows([w["dq"], w["dkv"]])
+        self.q_off, self.kv_off = offs
+        self.q_norm, self.kv_norm = w["dq.norm"].contiguous(), w["dkv.norm"].contiguous()
+        self.uq = w["uq"].contiguous()                                           # [H·(dim + rot_dim), q_rank]
+        self.uk_t = w["uk"].view(s.heads, s.dim, s.kv_rank).transpose(1, 2).contiguous()    # [H, kv_rank, dim]
+        self.uv = w["uv"].view(s.heads, s.vdim, s.kv_rank).contiguous()          # [H, vdim, kv_rank]
+        self.wo = w["o"].contiguous()
+        self.dtype = self.wo.dtype
+        self.row = s.kv_rank + s.rot_dim
+
+    def weights(self) -> List[torch.Tensor]:
+        return [self.w_in, self.q_norm, self.kv_norm, self.uq, self.uk_t, self.uv, self.wo]
+
+    def new_cache(self, batch: int, length: int, device: torch.device) -> Tuple[torch.Tensor, None]:
+        return torch.zeros((batch, length, self.row), dtype=self.dtype, device=device), None
+
+    def new_state(self, batch: int, device: torch.device) -> Optional[torch.Tensor]:
+        return None
+
+    def run(self, h: torch.Tensor, B: int, S: int, cache: "object", layer: int, rope: Tuple[torch.Tensor, torch.Tensor]
+            ) -> torch.Tensor:
+        s = self.spec
+        M, H, qd = B * S, s.heads, s.dim + s.rot_dim
+        rot = s.rot.dims if s.rot is not None else 0
+        layout = SK.ROT_LAYOUTS[s.rot.layout] if s.rot is not None else 0
+        kc = cache.ks[layer]                                                   # [B, T, kv_rank + rot_dim]
+        y = SK.linear(h, self.w_in)                                            # fp32 [M, query latent | kv latent | key part]
+        cq = SK.latent_prep(y, self.q_off, s.q_rank, self.kv_off, s.kv_rank, s.rot_dim, rot, layout, self.q_norm,
+                            self.kv_norm, kc, rope[0], rope[1], self.eps, cache.len_dev, cache.pad_left, B, S)
+        q = SK.linear(cq, self.uq, out_f32=False)                              # [M, H·(dim + rot_dim)]
+        qa = torch.empty((M, H * self.row), dtype=self.dtype, device=h.device)
+        SK.linear_batched(q, self.uk_t, qa, nbatch=H, rows=M, x_bs=qd, o_bs=self.row)      # U_hᵀ a_h
+        if s.rot_dim:
+            SK.rotary_slice(q, qd, s.dim, qa, self.row, s.kv_rank, H, s.rot_dim, rot, layout, rope[0], rope[1],
+                            cache.len_dev, cache.pad_left, B, S)
+        ctx = SK.attn_windowed(qa, kc, kc, cache.len_dev, cache.pad_left, B, S, H, 1, self.row, s.kv_rank, kc.shape[1],
+                               self.row, self.row, s.window, s.scale)         # [M, H·kv_rank]
+        out = torch.empty((M, H * s.vdim), dtype=self.dtype, device=h.device)
+        SK.linear_batched(ctx, self.uv, out, nbatch=H, rows=M, x_bs=s.kv_rank, o_bs=s.vdim)
+        return out
+
+
+class RetentionMixer:
+    """Retention: linear attention with one fixed decay per head, S_t = decay_h S_(t-1) + k_t v_tᵀ, o_t = S_tᵀ q_t, rotary
+    q / k, k scaled by dim^(-1/2) after the rotation; every head's read-out divided by its RMS (no weight) and gated by
+    silu of a projection of the input.  The fp32 state is what the layer keeps between tokens."""
+
+    kind = "retention"
+
+    def __init__(self, spec: RetentionMixerSpec, w: Dict[str, torch.Tensor], eps: float):
+        self.spec, self.eps = spec, float(eps)
+        self.w_in, offs = _stack_rows([w["q"], w["k"], w["v"], w["g"]])
+        self.q_off, self.k_off, self.v_off, self.g_off = offs
+        self.wo = w["o"].contiguous()
+        self.dtype = self.wo.dtype
+        self.decay = torch.tensor([float(a) for a in spec.decay], dtype=torch.float64).to(torch.float32).to(self.wo.device)
+
+    def weights(self) -> List[torch.Tensor]:
+        return [self.w_in, self.wo]
+
+    def new_cache(self, batch: int, length: int, device: torch.device) -> None:
+        return None
+
+    def new_state(self, batch: int, device: torch.device) -> torch.Tensor:
+        s = self.spec
+        return torch.zeros((batch, s.heads, s.dim, s.vdim), dtype=torch.float32, device=device)
+
+    def run(self, h: torch.Tensor, B: int, S: int, cache: "object", layer: int, rope: Tuple[torch.Tensor, torch.Tensor]
+            ) -> torch.Tensor:
+        s = self.spec
+        rot = s.rot.dims if s.rot is not None else 0
+        layout = SK.ROT_LAYOUTS[s.rot.layout] if s.rot is not None else 0
+        y = SK.linear(h, self.w_in)                                   # fp32 [M, q | k | v | gate]
+        o = SK.retention_scan(y, self.q_off, self.k_off, self.v_off, self.decay, rope[0], rope[1], rot, layout,
+                              s.dim ** -0.5, cache.states[layer], cache.len_dev, cache.pad_left, B, S, s.heads, s.dim,
+                              s.vdim)
+        gate = y[:, self.g_off:self.g_off + s.heads * s.vdim]
+        return SK.headnorm_gate(o, None, gate, s.heads, s.vdim, self.eps, SK.ACT_SILU, dtype=self.dtype)
+
+
+MIXERS = {"attention": AttentionMixer, "gla": GlaMixer, "latent_attention": LatentAttentionMixer,
+          "retention": RetentionMixer}
+

@@ -9,7 +9,7 @@ import json
 import os
 from typing import Any, Callable, Dict, Optional, Tuple
 
-from ..config import CONFIG_NAME, FoliraxConfig, LLaMAConfig
+from ..config import CONFIG_NAME, FoliraxConfig, LLaMAConfig, NikonexConfig
 
 _REGISTRY: Dict[str, Tuple[Any, Callable[[], Any]]] = {}
 _KERNEL_SUBSET: Dict[str, Optional[str]] = {}
@@ -44,8 +44,14 @@ def _folirax() -> Any:
     return FoliraxForCausalLM
 
 
+def _nikonex() -> Any:
+    from .nikonex import NikonexForCausalLM
+    return NikonexForCausalLM
+
+
 register("llama", LLaMAConfig, _llama)
 register("folirax", FoliraxConfig, _folirax, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
+register("nikonex", NikonexConfig, _nikonex, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
 
 
 def architecture_of(config: Dict[str, Any]) -> str:

@@ -14,7 +14,7 @@ from .build import LIB_PATH, build_library
 _lib: Optional[C.CDLL] = None
 
 vp, ip, fp = C.c_void_p, C.c_void_p, C.c_void_p   # all pointers travel as integers from tensor.data_ptr()
-i32, f32, u64, sz = C.c_int, C.c_float, C.c_ulonglong, C.c_size_t
+i32, f32, u64, sz, i64 = C.c_int, C.c_float, C.c_ulonglong, C.c_size_t, C.c_longlong
 
 _SIGNATURES = {
     "jl_last_error": (C.c_char_p, []),
@@ -68,6 +68,18 @@ _HYBRID = {
     "jl_head_gate": (i32, [vp, fp, i32, i32, i32, i32, i32, vp]),
     "jl_gla_scan": (i32, [fp, i32, i32, i32, i32, i32, vp, vp, fp, fp, ip, ip] + [i32] * 6 + [f32, f32, fp, i32, vp]),
     "jl_gla_scan_ws_floats": (sz, [i32, i32, i32, i32, i32]),
+    "jl_retention_scan": (i32, [fp, i32, i32, i32, i32, fp, fp, fp, i32, i32, i32, f32, f32, fp, fp, ip, ip] + [i32] * 5 + [fp, vp]),
+    "jl_branch_add_norm": (i32, [fp, i32, fp, i32, f32, fp, vp, vp, vp, vp, i32, i32, f32, i32, vp]),
+    "jl_linear_tile_rows": (i32, []),
+    "jl_linear_grouped": (i32, [vp, i32, i64, vp, i64, vp, i32, i64, i32, i32, i32, i32, i32, i32, f32, f32, ip, ip, ip, i32, i32,
+                                vp]),
+    "jl_attn_windowed": (i32, [vp, vp, vp, vp, ip, ip] + [i32] * 10 + [f32, fp, i32, i32, vp]),
+    "jl_latent_prep": (i32, [fp] + [i32] * 8 + [vp, vp, vp, vp, fp, fp, i32, f32, ip, ip, i32, i32, i32, i32, vp]),
+    "jl_rotary_slice": (i32, [vp, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, fp, fp, i32, ip, ip, i32, i32, i32, vp]),
+    "jl_moe_route": (i32, [fp] + [i32] * 9 + [f32, ip, fp, vp]),
+    "jl_moe_sorted_rows": (i32, [i32, i32, i32]),
+    "jl_moe_sort": (i32, [ip] + [i32] * 5 + [ip, ip, ip, vp]),
+    "jl_moe_combine": (i32, [fp, i32, ip, fp, i32, fp, i32, fp, i32, fp, i32, i32, vp]),
 }
 
 _OPTIONAL = {

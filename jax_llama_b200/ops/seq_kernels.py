@@ -77,16 +77,19 @@ def postnorm_add(y: torch.Tensor, w_post: torch.Tensor, x: torch.Tensor, eps: fl
     return h_out if w_next is not None else None
 
 
-def headnorm_gate(o: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, H: int, V: int, eps: float,
-                  gate_act: int = ACT_SILU, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """o fp32 [M, H·V]; gate: fp32 view [M, H·V] (any row pitch) → norm over V per head · w · act(gate), w's dtype."""
+def headnorm_gate(o: torch.Tensor, w: Optional[torch.Tensor], gate: torch.Tensor, H: int, V: int, eps: float,
+                  gate_act: int = ACT_SILU, out: Optional[torch.Tensor] = None, dtype: Optional[torch.dtype] = None
+                  ) -> torch.Tensor:
+    """o fp32 [M, H·V]; gate: fp32 view [M, H·V] (any row pitch) → norm over V per head · w · act(gate), in w's dtype
+    (w None: no weight, the result in `dtype`)."""
     _need(o, torch.float32, "o")
     _need(gate, torch.float32, "gate")
     M = o.shape[0]
+    odt = w.dtype if w is not None else dtype
     if out is None:
-        out = torch.empty((M, H * V), dtype=w.dtype, device=o.device)
-    _lib.check(_lib.lib().jl_headnorm_gate(o.data_ptr(), w.data_ptr(), gate.data_ptr(), gate.stride(0), out.data_ptr(),
-                                           M, H, V, float(eps), gate_act, dtype_code(w.dtype), _stream()),
+        out = torch.empty((M, H * V), dtype=odt, device=o.device)
+    _lib.check(_lib.lib().jl_headnorm_gate(o.data_ptr(), _p(w), gate.data_ptr(), gate.stride(0), out.data_ptr(),
+                                           M, H, V, float(eps), gate_act, dtype_code(odt), _stream()),
                "jl_headnorm_gate")
     return out
 
@@ -197,4 +200,164 @@ def gla_scan(y: torch.Tensor, q_off: int, k_off: int, v_off: int, a_off: int, a2
         y.data_ptr(), y.stride(0), q_off, k_off, v_off, a_off, a2.data_ptr(), a2_bias.data_ptr(), state.data_ptr(),
         out.data_ptr(), _p(cache_len), _p(pad_left), B, S, H, D, Dv, R, float(q_scale), float(tau), _p(ws),
         dtype_code(a2.dtype), _stream()), "jl_gla_scan")
+    return out
+
+
+# --------------------------------------------------------------------------- parallel blocks, latent attention, retention, experts
+ROT_INTERLEAVED, ROT_HALF = 0, 1        # channel 2i with 2i+1 / channel i with i + dims/2
+ROT_LAYOUTS = {"interleaved": ROT_INTERLEAVED, "half": ROT_HALF}
+SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1
+SCORES = {"sigmoid": SCORE_SIGMOID, "softmax": SCORE_SOFTMAX}
+MOE_PAIR_ROWS = 16                      # up to this many token rows every (token, choice) pair streams its own expert
+
+
+def branch_add_norm(x: torch.Tensor, y1: Optional[torch.Tensor], y2: Optional[torch.Tensor], mult: float,
+                    w1: Optional[torch.Tensor], w2: Optional[torch.Tensor], eps: float
+                    ) -> "tuple[Optional[torch.Tensor], Optional[torch.Tensor]]":
+    """x += mult · (y1 + y2) in place (fp32; either branch may be None), then h1 = norm(x) · w1 and h2 = norm(x) · w2
+    for the weights given (plain weights, the weights' dtype)."""
+    _need(x, torch.float32, "x")
+    M, W = x.shape
+    for y in (y1, y2):
+        if y is not None:
+            _need(y, torch.float32, "y")
+    h1 = torch.empty((M, W), dtype=w1.dtype, device=x.device) if w1 is not None else None
+    h2 = torch.empty((M, W), dtype=w2.dtype, device=x.device) if w2 is not None else None
+    if y1 is None and y2 is None and w1 is None and w2 is None:
+        return None, None
+    dt = w1.dtype if w1 is not None else (w2.dtype if w2 is not None else torch.float32)
+    _lib.check(_lib.lib().jl_branch_add_norm(_p(y1), y1.stride(0) if y1 is not None else 0, _p(y2),
+                                             y2.stride(0) if y2 is not None else 0, float(mult), x.data_ptr(), _p(w1), _p(h1),
+                                             _p(w2), _p(h2), M, W, float(eps), dtype_code(dt), _stream()), "jl_branch_add_norm")
+    return h1, h2
+
+
+def linear_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, nbatch: int, rows: int, x_bs: int, o_bs: int,
+                   x_div: int = 1, w_index: Optional[torch.Tensor] = None, act: int = ACT_NONE) -> torch.Tensor:
+    """`nbatch` products act(x_z W_zᵀ) of `rows` rows each: x_z starts (z // x_div) · x_bs elements into x (row pitch
+    x.stride(0)), W_z = w[w_index[z]] or w[z] (w [n, N, K]), the result goes o_bs · z elements into out (row pitch
+    out.stride(0); fp32 or the operand type)."""
+    _need(w, x.dtype, "w")
+    _, N, K = w.shape
+    _lib.check(_lib.lib().jl_linear_grouped(
+        x.data_ptr(), x.stride(0), int(x_bs), w.data_ptr(), N * K, out.data_ptr(), out.stride(0), int(o_bs), int(nbatch),
+        int(x_div), int(rows), N, K, act, 0.0, 0.0, _p(w_index), 0, 0, dtype_code(x.dtype), int(out.dtype == torch.float32),
+        _stream()), "jl_linear_grouped")
+    return out
+
+
+def linear_sorted(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,
+                  row_src: Optional[torch.Tensor], act: int = ACT_NONE) -> torch.Tensor:
+    """Rows sorted by weight matrix: out[p] = act(W_g x[row_src[p]]) with g = tile_group[p // tile] (w [n, N, K])."""
+    _need(w, x.dtype, "w")
+    _, N, K = w.shape
+    _lib.check(_lib.lib().jl_linear_grouped(
+        x.data_ptr(), x.stride(0), 0, w.data_ptr(), N * K, out.data_ptr(), out.stride(0), 0, 1, 1, out.shape[0], N, K, act,
+        0.0, 0.0, 0, tile_group.data_ptr(), _p(row_src), dtype_code(x.dtype), int(out.dtype == torch.float32), _stream()),
+        "jl_linear_grouped")
+    return out
+
+
+def latent_prep(y: torch.Tensor, q_off: int, q_rank: int, kv_off: int, kv_rank: int, rot_dim: int, rot: int, layout: int,
+                wq_norm: Optional[torch.Tensor], wkv_norm: torch.Tensor, cache: torch.Tensor, cos: torch.Tensor,
+                sin: torch.Tensor, eps: float, cache_len: torch.Tensor, pad_left: Optional[torch.Tensor], B: int, S: int
+                ) -> Optional[torch.Tensor]:
+    """Norm both latents, rotate the shared key part, append [latent | key part] to cache [B, T, kv_rank + rot_dim];
+    returns the normed query latent [B·S, q_rank] (None when q_rank == 0)."""
+    _need(y, torch.float32, "y")
+    cq = torch.empty((B * S, q_rank), dtype=cache.dtype, device=y.device) if q_rank else None
+    _lib.check(_lib.lib().jl_latent_prep(
+        y.data_ptr(), y.stride(0), q_off, q_rank, kv_off, kv_rank, rot_dim, rot, layout, _p(wq_norm), wkv_norm.data_ptr(),
+        _p(cq), cache.data_ptr(), cos.data_ptr(), sin.data_ptr(), cos.shape[0], float(eps), _p(cache_len), _p(pad_left), B, S,
+        cache.shape[1], dtype_code(cache.dtype), _stream()), "jl_latent_prep")
+    return cq
+
+
+def rotary_slice(src: torch.Tensor, in_hs: int, in_off: int, out: torch.Tensor, out_hs: int, out_off: int, H: int, n: int,
+                 rot: int, layout: int, cos: torch.Tensor, sin: torch.Tensor, cache_len: torch.Tensor,
+                 pad_left: Optional[torch.Tensor], B: int, S: int) -> torch.Tensor:
+    _need(out, src.dtype, "out")
+    _lib.check(_lib.lib().jl_rotary_slice(
+        src.data_ptr(), src.stride(0), in_hs, in_off, out.data_ptr(), out.stride(0), out_hs, out_off, H, n, rot, layout,
+        cos.data_ptr(), sin.data_ptr(), cos.shape[0], _p(cache_len), _p(pad_left), B, S, dtype_code(src.dtype), _stream()),
+        "jl_rotary_slice")
+    return out
+
+
+def attn_windowed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_len: torch.Tensor,
+                  pad_left: Optional[torch.Tensor], B: int, S: int, H: int, G: int, D: int, Dv: int, T_cap: int, ldk: int,
+                  ldv: int, window: int, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of S new tokens per row over cache rows of pitch ldk / ldv (keys and values may be columns of
+    one cached row; caches [B, G, T_cap, ·]); window > 0 keeps the last `window` slots up to the query's own."""
+    if out is None:
+        out = torch.empty((B * S, H * Dv), dtype=q.dtype, device=q.device)
+    L = _lib.lib()
+    splits, scratch = 0, None
+    if S == 1:
+        splits = int(L.jl_attn_generic_splits(B, H, G, min(T_cap, window) if window > 0 else T_cap))
+        if splits:
+            scratch = torch.empty(B * H * splits * (Dv + 2), dtype=torch.float32, device=q.device)
+    _lib.check(L.jl_attn_windowed(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(cache_len), _p(pad_left), B, S, H, G, D, Dv,
+        T_cap, ldk, ldv, int(window), float(scale), _p(scratch), splits, dtype_code(q.dtype), _stream()), "jl_attn_windowed")
+    return out
+
+
+def retention_scan(y: torch.Tensor, q_off: int, k_off: int, v_off: int, head_decay: torch.Tensor, cos: torch.Tensor,
+                   sin: torch.Tensor, rot: int, layout: int, k_scale: float, state: torch.Tensor,
+                   cache_len: Optional[torch.Tensor], pad_left: Optional[torch.Tensor], B: int, S: int, H: int, D: int,
+                   Dv: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Advance the fp32 state [B, H, D, Dv] over S tokens per row with one fixed decay per head (fp32 [H]), q and k
+    rotated at the token's position, k scaled after the rotation; returns the raw read-outs fp32 [B·S, H·Dv]."""
+    _need(y, torch.float32, "y")
+    _need(state, torch.float32, "state")
+    _need(head_decay, torch.float32, "head_decay")
+    if out is None:
+        out = torch.empty((B * S, H * Dv), dtype=torch.float32, device=y.device)
+    L = _lib.lib()
+    ws = None
+    if S > GLA_FUSED_MAX_TOKENS:
+        ws = torch.empty(int(L.jl_gla_scan_ws_floats(B, S, H, D, Dv)), dtype=torch.float32, device=y.device)
+    _lib.check(L.jl_retention_scan(
+        y.data_ptr(), y.stride(0), q_off, k_off, v_off, head_decay.data_ptr(), cos.data_ptr(), sin.data_ptr(), cos.shape[0],
+        rot, layout, 1.0, float(k_scale), state.data_ptr(), out.data_ptr(), _p(cache_len), _p(pad_left), B, S, H, D, Dv,
+        _p(ws), _stream()), "jl_retention_scan")
+    return out
+
+
+def moe_route(z: torch.Tensor, E: int, top: int, groups: int, keep: int, group_top: int, score: int, normalise: bool,
+              scale: float) -> "tuple[torch.Tensor, torch.Tensor]":
+    """fp32 router logits (columns 0..E-1 of z) → (experts int32 [M, top], weights fp32 [M, top])."""
+    _need(z, torch.float32, "z")
+    M = z.shape[0]
+    idx = torch.empty((M, top), dtype=torch.int32, device=z.device)
+    wt = torch.empty((M, top), dtype=torch.float32, device=z.device)
+    _lib.check(_lib.lib().jl_moe_route(z.data_ptr(), z.stride(0), M, E, top, groups, keep, group_top, score, int(normalise),
+                                       float(scale), idx.data_ptr(), wt.data_ptr(), _stream()), "jl_moe_route")
+    return idx, wt
+
+
+def moe_sort(idx: torch.Tensor, E: int) -> "tuple[torch.Tensor, torch.Tensor, torch.Tensor]":
+    """(pos int32 [M·top], row_src int32 [rows], tile_group int32 [rows / tile]) of the pairs ordered by expert."""
+    L = _lib.lib()
+    M, top = idx.shape
+    tile = int(L.jl_linear_tile_rows())
+    cap = int(L.jl_moe_sorted_rows(M * top, E, tile))
+    pos = torch.empty(M * top, dtype=torch.int32, device=idx.device)
+    row_src = torch.empty(cap, dtype=torch.int32, device=idx.device)
+    tile_group = torch.empty(cap // tile, dtype=torch.int32, device=idx.device)
+    _lib.check(L.jl_moe_sort(idx.data_ptr(), M, top, E, tile, cap, pos.data_ptr(), row_src.data_ptr(), tile_group.data_ptr(),
+                             _stream()), "jl_moe_sort")
+    return pos, row_src, tile_group
+
+
+def moe_combine(z: torch.Tensor, pos: Optional[torch.Tensor], wt: torch.Tensor, shared: Optional[torch.Tensor],
+                gate: Optional[torch.Tensor], W: int) -> torch.Tensor:
+    """Σ_k wt[m, k] · z[pos[m, k]] (+ sigmoid(gate[m]) · shared[m]) → fp32 [M, W]; gate: fp32 view [M, 1] (any pitch)."""
+    M, top = wt.shape
+    out = torch.empty((M, W), dtype=torch.float32, device=z.device)
+    _lib.check(_lib.lib().jl_moe_combine(z.data_ptr(), z.stride(0), _p(pos), wt.data_ptr(), top, _p(shared),
+                                         shared.stride(0) if shared is not None else 0, _p(gate),
+                                         gate.stride(0) if gate is not None else 0, out.data_ptr(), M, W, _stream()),
+               "jl_moe_combine")
     return out
