@@ -740,7 +740,7 @@ class B200Engine:
             return st.graphs[key]
         # warm up outside capture on a side stream (first-use initialisation, cudaFuncSetAttribute, …);
         # the step is re-playable because a snapshot of the mutable state is restored afterwards
-        mutable = (st.ids, st.finished, st.sequences, st.cur_len, st.step, st.n_unfinished, *cache.mutable_state())
+        mutable = (st.ids, st.finished, st.sequences, st.cur_len, st.step, st.n_unfinished, st.logits, *cache.mutable_state())
         snap = [t.clone() for t in mutable]
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
