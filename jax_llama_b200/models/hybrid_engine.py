@@ -205,7 +205,7 @@ class HybridEngine(B200Engine):
             sc = rot.scaling
             key = (int(rot.dims), float(rot.base), None if sc is None else (sc.factor, sc.original, sc.fast, sc.slow))
         have = self._rope.get(key)
-        if have is None or have[0].shape[0] < length:
+        if have is None or (rot is not None and have[0].shape[0] < length):
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("rotary table too short for a captured step: size it before the capture")
             self._rope[key] = have = rotary_table(key[0], key[1], max(length, 256) if rot is not None else 1, self.device,
