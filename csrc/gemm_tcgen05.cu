@@ -45,6 +45,11 @@ struct GemmParams {
   int* tickets;                      // [2][ticket_half]: arrivals, completions per tile; zero between launches
   int ticket_half;
   unsigned long long* trace;         // optional [grid][16] %globaltimer stamps (jl_gemm_set_trace), NULL = off
+  // ---- grouped B operand (normal orientation only): the B tensor holds `groups` matrices of group_rows rows one after
+  // the other and A-tile a uses matrix tile_group[a] (< 0: a padding tile, any matrix will do — nobody reads its rows).
+  // The rows of A were ordered beforehand so that every 128-row tile belongs to one matrix (a mixture of experts).
+  const int* tile_group;
+  int group_rows;
 };
 
 __host__ __device__ constexpr int tmem_cols_for(int bn) {
@@ -138,6 +143,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int kb0 = split * num_kb / ksplit, kb1 = (split + 1) * num_kb / ksplit;
         const int b_blk = t / p.a_blocks;
         const int a_blk = t % p.a_blocks;
+        int b_row = b_blk * BN;
+        if constexpr (!SWAP) {
+          if (p.tile_group != nullptr) {
+            const int e = p.tile_group[a_blk];
+            b_row += (e < 0 ? 0 : e) * p.group_rows;
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           const uint32_t sa = smem_base + stage * STAGE_BYTES, sb = sa + A_BYTES;
           if (pre > 0) {
@@ -147,7 +159,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tc::mbar_expect_tx(full_bar(stage), A_BYTES + B_BYTES);
             tc::tma_load_2d(sa, &tmap_a, full_bar(stage), kb * GEMM_BK, a_blk * GEMM_BM, p.hint_a);
           }
-          tc::tma_load_2d(sb, &tmap_b, full_bar(stage), kb * GEMM_BK, b_blk * BN, p.hint_b);
+          tc::tma_load_2d(sb, &tmap_b, full_bar(stage), kb * GEMM_BK, b_row, p.hint_b);
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
       }
@@ -396,13 +408,13 @@ static SplitKWorkspace splitk_workspace() {
 
 template <int BN, int EPI, bool SWAP, bool OUT_F32>
 static int launch_gemm(const void* a, const void* b, const GemmParams& p0, int Ra, int Rb, int K, int num_sms,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, int b_matrices = 1) {
   GemmParams p = p0;
   p.trace = g_gemm_trace;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d_bf16(&ta, a, Ra, K, K, GEMM_BM);
   if (rc) return rc;
-  rc = make_tmap_2d_bf16(&tb, b, Rb, K, K, BN);
+  rc = make_tmap_2d_bf16(&tb, b, Rb * b_matrices, K, K, BN);
   if (rc) return rc;
   constexpr uint32_t A_BYTES = GEMM_BM * GEMM_BK * 2;
   constexpr uint32_t B_BYTES = BN * GEMM_BK * 2;
@@ -514,4 +526,29 @@ extern "C" JL_API int jl_gemm(const void* x, const void* w, const void* residual
   if (mode == EPI_PLAIN) return dispatch_gemm<EPI_PLAIN, false>(x, w, p, M, N, K, num_sms, s);
   if (mode == EPI_RESIDUAL) return dispatch_gemm<EPI_RESIDUAL, false>(x, w, p, M, N, K, num_sms, s);
   return dispatch_gemm<EPI_SWIGLU, false>(x, w, p, M, N, K, num_sms, s);
+}
+
+// Grouped form of the token-major GEMM: x [M, K] with M a multiple of 128 and every 128-row tile belonging to one of
+// `groups` weight matrices w [groups][N, K]; out[m] = W_(tile_group[m / 128]) x[m] (bf16 or fp32, row pitch N).
+extern "C" JL_API int jl_gemm_grouped(const void* x, const void* w, void* out, int M, int N, int K, int groups,
+                                      const int* tile_group, int out_f32, int num_sms, void* stream) {
+  JL_CHECK_ARG(M >= GEMM_BM && M % GEMM_BM == 0, "jl_gemm_grouped: M=%d must be a multiple of %d", M, GEMM_BM);
+  JL_CHECK_ARG(N >= 8 && N % 8 == 0 && K >= 8 && K % 8 == 0 && groups >= 1 && tile_group != nullptr,
+               "jl_gemm_grouped: bad shape N=%d K=%d groups=%d", N, K, groups);
+  if (num_sms <= 0) num_sms = 148;
+  GemmParams p{};
+  p.out = out;
+  p.K = K;
+  p.ldo = N;
+  p.Ra = M; p.Rb = N;
+  p.hint_a = tc::EVICT_NORMAL; p.hint_b = tc::EVICT_LAST;
+  p.tile_group = tile_group;
+  p.group_rows = N;
+  auto s = (cudaStream_t)stream;
+  if (out_f32) {
+    if (N >= 256) return launch_gemm<256, EPI_PLAIN, false, true>(x, w, p, M, N, K, num_sms, s, groups);
+    return launch_gemm<128, EPI_PLAIN, false, true>(x, w, p, M, N, K, num_sms, s, groups);
+  }
+  if (N >= 256) return launch_gemm<256, EPI_PLAIN, false, false>(x, w, p, M, N, K, num_sms, s, groups);
+  return launch_gemm<128, EPI_PLAIN, false, false>(x, w, p, M, N, K, num_sms, s, groups);
 }

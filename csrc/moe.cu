@@ -162,6 +162,24 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
   }
 }
 
+// xs[p, :] = x[row_src[p], :] (row_src[p] < 0: zeros): the rows of a step in sorted order, for kernels that cannot gather.
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gather_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ row_src,
+                                                         T* __restrict__ xs, int W) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
+  const size_t p = blockIdx.x;
+  const int src = row_src[p];
+  constexpr int VN = 16 / sizeof(T);
+  if (W % VN == 0 && ldx % VN == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)xs & 15) == 0) {
+    const uint4* in = src >= 0 ? reinterpret_cast<const uint4*>(x + (size_t)src * ldx) : nullptr;
+    uint4* out = reinterpret_cast<uint4*>(xs + p * W);
+    for (int i = threadIdx.x; i < W / VN; i += blockDim.x) out[i] = in ? in[i] : make_uint4(0, 0, 0, 0);
+    return;
+  }
+  for (int i = threadIdx.x; i < W; i += blockDim.x) xs[p * W + i] = src >= 0 ? x[(size_t)src * ldx + i] : from_f<T>(0.0f);
+}
+
 }  // namespace jl
 
 using namespace jl;
@@ -199,6 +217,13 @@ extern "C" JL_API int jl_moe_combine(const float* z, int ldz, const int* pos, co
                                      const float* gate, int ldg, float* out, int M, int W, void* stream) {
   JL_CHECK_ARG(M >= 1 && W >= 1 && top >= 1 && ldz >= W, "jl_moe_combine: bad shape");
   JL_LAUNCH_PDL(moe_combine_kernel, dim3(M), dim3(256), 0, stream, z, ldz, pos, wt, top, shared, lds, gate, ldg, out, W);
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+extern "C" JL_API int jl_moe_gather(const void* x, int ldx, const int* row_src, void* xs, int rows, int W, int dtype, void* stream) {
+  JL_CHECK_ARG(rows >= 1 && W >= 1 && ldx >= W, "jl_moe_gather: bad shape");
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(moe_gather_kernel<T>, dim3(rows), dim3(128), 0, stream, (const T*)x, ldx, row_src, (T*)xs, W));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

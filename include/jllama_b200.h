@@ -354,6 +354,12 @@ int jl_moe_sort(const int* idx, int M, int top, int E, int tile, int cap, int* p
 /* out[m] = sum_k wt[m, k] * z[pos ? pos[m*top+k] : m*top+k] (+ (gate ? sigmoid(gate[m*ldg]) : 1) * shared[m] when shared). */
 int jl_moe_combine(const float* z, int ldz, const int* pos, const float* wt, int top, const float* shared, int lds,
                    const float* gate, int ldg, float* out, int M, int W, void* stream);
+/* xs[p] = x[row_src[p]] (zeros where row_src[p] < 0): the rows of a step in sorted order; rows x W of dtype. */
+int jl_moe_gather(const void* x, int ldx, const int* row_src, void* xs, int rows, int W, int dtype, void* stream);
+/* Grouped token-major tcgen05 GEMM: x bf16 [M, K], M a multiple of 128, every 128-row tile t using the weight matrix
+ * w[tile_group[t]] of w bf16 [groups][N, K] (< 0: a padding tile); out [M, N] bf16 or fp32.  N % 8 == 0, K % 8 == 0. */
+int jl_gemm_grouped(const void* x, const void* w, void* out, int M, int N, int K, int groups, const int* tile_group,
+                    int out_f32, int num_sms, void* stream);
 
 #ifdef __cplusplus
 }

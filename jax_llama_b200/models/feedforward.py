@@ -46,7 +46,9 @@ class MoeFeedForward:
     """Mixture of experts.  The router (and the shared expert's gate) is one fp32-accumulated product; a warp per
     token chooses the experts.  Few rows (decoding): every (token, choice) pair streams its expert's two matrices in
     one batched launch each.  Many rows (prompts): the pairs are ordered by expert into whole row tiles and each tile
-    runs against its expert's matrices.  The weighted sum, the shared expert and its gate meet in one combine pass."""
+    runs against its expert's matrices — in bfloat16 on the grouped tcgen05 GEMM over rows gathered once, otherwise
+    (true float32, sizes the tensor-core kernel does not take) on the exact tiled kernel, which gathers as it reads.
+    The weighted sum, the shared expert and its gate meet in one combine pass."""
 
     kind = "moe"
 
@@ -99,6 +101,12 @@ class MoeFeedForward:
             y = torch.empty((n, W), dtype=torch.float32, device=h.device)
             SK.linear_batched(t, self.down, y, nbatch=n, rows=1, x_bs=s.ff, o_bs=W, w_index=flat)
             pos = None
+        elif SK.tensor_cores_enabled() and h.dtype == torch.bfloat16 and W % 8 == 0 and s.ff % 8 == 0 and h.is_contiguous():
+            # sorted rows in 128-row segments, gathered once, then the grouped tcgen05 GEMM twice
+            pos, row_src, tile_group = SK.moe_sort(idx, s.experts, tile=SK.GEMM_TILE_ROWS)
+            xs = SK.moe_gather(h, row_src)
+            t = SK.gemm_grouped(xs, self.up, tile_group, act=self.act, out_f32=False)
+            y = SK.gemm_grouped(t, self.down, tile_group)
         else:
             pos, row_src, tile_group = SK.moe_sort(idx, s.experts)
             rows = row_src.shape[0]

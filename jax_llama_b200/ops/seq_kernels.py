@@ -337,11 +337,12 @@ def moe_route(z: torch.Tensor, E: int, top: int, groups: int, keep: int, group_t
     return idx, wt
 
 
-def moe_sort(idx: torch.Tensor, E: int) -> "tuple[torch.Tensor, torch.Tensor, torch.Tensor]":
-    """(pos int32 [M·top], row_src int32 [rows], tile_group int32 [rows / tile]) of the pairs ordered by expert."""
+def moe_sort(idx: torch.Tensor, E: int, tile: Optional[int] = None) -> "tuple[torch.Tensor, torch.Tensor, torch.Tensor]":
+    """(pos int32 [M·top], row_src int32 [rows], tile_group int32 [rows / tile]) of the pairs ordered by expert, every
+    expert's segment rounded up to `tile` rows (default: the row tile of the SIMT grouped linear)."""
     L = _lib.lib()
     M, top = idx.shape
-    tile = int(L.jl_linear_tile_rows())
+    tile = int(L.jl_linear_tile_rows()) if tile is None else int(tile)
     cap = int(L.jl_moe_sorted_rows(M * top, E, tile))
     pos = torch.empty(M * top, dtype=torch.int32, device=idx.device)
     row_src = torch.empty(cap, dtype=torch.int32, device=idx.device)
@@ -349,6 +350,36 @@ def moe_sort(idx: torch.Tensor, E: int) -> "tuple[torch.Tensor, torch.Tensor, to
     _lib.check(L.jl_moe_sort(idx.data_ptr(), M, top, E, tile, cap, pos.data_ptr(), row_src.data_ptr(), tile_group.data_ptr(),
                              _stream()), "jl_moe_sort")
     return pos, row_src, tile_group
+
+
+GEMM_TILE_ROWS = 128                    # row tile of the tcgen05 GEMM: the segment size of the grouped form
+
+
+def moe_gather(x: torch.Tensor, row_src: torch.Tensor) -> torch.Tensor:
+    """xs[p] = x[row_src[p]] (zeros where row_src[p] < 0)."""
+    W = x.shape[1]
+    xs = torch.empty((row_src.shape[0], W), dtype=x.dtype, device=x.device)
+    _lib.check(_lib.lib().jl_moe_gather(x.data_ptr(), x.stride(0), row_src.data_ptr(), xs.data_ptr(), row_src.shape[0], W,
+                                        dtype_code(x.dtype), _stream()), "jl_moe_gather")
+    return xs
+
+
+def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, *, act: int = ACT_NONE, out_f32: bool = True
+                 ) -> torch.Tensor:
+    """tcgen05 GEMM over sorted rows: x bf16 [rows, K] (rows a multiple of 128, contiguous), w bf16 [n, N, K]; 128-row
+    tile t runs against w[tile_group[t]].  The activation is an in-place pass over the stored result."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    n, N, K = w.shape
+    rows = x.shape[0]
+    out = torch.empty((rows, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    L = _lib.lib()
+    _lib.check(L.jl_gemm_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), rows, N, K, n, tile_group.data_ptr(),
+                                 int(out_f32), num_sms(x.device), _stream()), "jl_gemm_grouped")
+    if act != ACT_NONE:
+        _lib.check(L.jl_act_inplace(out.data_ptr(), out.stride(0), rows, N, act, 0.0, 0.0, dtype_code(out.dtype), _stream()),
+                   "jl_act_inplace")
+    return out
 
 
 def moe_combine(z: torch.Tensor, pos: Optional[torch.Tensor], wt: torch.Tensor, shared: Optional[torch.Tensor],
