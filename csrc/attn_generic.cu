@@ -88,6 +88,7 @@ struct LatentPrepParams {
   float eps;
   int B, S, T;
   const int* cache_len; const int* pad_left;
+  void* c_out; void* kr_out;        // optional token-major copies of what was appended: latent [M][kv_rank], key part [M][rot_dim]
 };
 
 template <typename T>
@@ -112,12 +113,21 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(LatentPrepParams p, co
   float ss = 0.0f;
   for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) { const float v = yr[p.kv_off + i]; ss += v * v; }
   const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)p.kv_rank + p.eps);
-  for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) row[i] = from_f<T>(yr[p.kv_off + i] * r * to_f(wkv[i]));
+  T* c_out = p.c_out ? (T*)p.c_out + (size_t)m * p.kv_rank : nullptr;
+  T* kr_out = p.kr_out ? (T*)p.kr_out + (size_t)m * p.rot_dim : nullptr;
+  for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) {
+    const T v = from_f<T>(yr[p.kv_off + i] * r * to_f(wkv[i]));
+    row[i] = v;
+    if (c_out) c_out[i] = v;
+  }
   const float* src = yr + p.kv_off + p.kv_rank;
   const float* ct = p.cos_t + (size_t)pos * (p.rot / 2);
   const float* st = p.sin_t + (size_t)pos * (p.rot / 2);
-  for (int d = threadIdx.x; d < p.rot_dim; d += blockDim.x)
-    row[p.kv_rank + d] = from_f<T>(rotary_channel(src, d, p.rot, p.layout, ct, st));
+  for (int d = threadIdx.x; d < p.rot_dim; d += blockDim.x) {
+    const T v = from_f<T>(rotary_channel(src, d, p.rot, p.layout, ct, st));
+    row[p.kv_rank + d] = v;
+    if (kr_out) kr_out[d] = v;
+  }
 }
 
 // out[m, h, out_off + d] = rotary(in[m, h, in_off + d]), d < n: a slice of every head rotated at the token's position and
@@ -146,6 +156,8 @@ __global__ void __launch_bounds__(128) rotary_slice_kernel(const T* __restrict__
 struct AttnParams {
   int B, S, H, G, D, Dv, T;
   int ldk, ldv;                     // row pitch of the key / value cache in elements (>= D / Dv: the two may be columns of one row)
+  long long k_bs, k_hs, v_bs, v_hs; // batch-row and key/value-head strides in elements: [B][G][T][ld] caches have bs = G*T*ld, hs = T*ld;
+                                    // token-major projections [B*T][G][ld'] have bs = T*G*ld', hs = ld' and a row pitch of G*ld'
   int window;                       // > 0: a query at slot i sees slots i - window + 1 .. i only; 0: everything before it
   float scale;
   const int* cache_len;             // slots already filled BEFORE this call's tokens (device scalar); nullptr = 0
@@ -197,21 +209,27 @@ template <typename T>
 __device__ __forceinline__ void stage_rows(float* dst, int pitch, const T* __restrict__ src, int n, int ld, int j0, int jmax) {
   constexpr int VN = 16 / sizeof(T);
   if (n % VN == 0 && ld % VN == 0 && ((uintptr_t)src & 15) == 0) {
-    const int per_row = n / VN;
-    for (int i = threadIdx.x; i < 32 * per_row; i += blockDim.x) {
-      const int r = i / per_row, cv = i % per_row, j = j0 + r;
-      float* d = dst + r * pitch + cv * VN;
-      if (j <= jmax) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)j * ld + cv * VN);
-        if constexpr (sizeof(T) == 2) {
-          *reinterpret_cast<float4*>(d) = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
-          *reinterpret_cast<float4*>(d + 4) = make_float4(bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w));
-        } else {
-          *reinterpret_cast<uint4*>(d) = raw;
-        }
-      } else {
+    const int per_row = n / VN, total = 32 * per_row;
+    constexpr int U = 4;                                   // loads in flight per thread: the tile is latency-bound otherwise
+    for (int i0 = threadIdx.x; i0 < total; i0 += U * blockDim.x) {
+      uint4 raw[U];
 #pragma unroll
-        for (int e = 0; e < VN; e += 4) *reinterpret_cast<float4*>(d + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * blockDim.x;
+        const int r = i / per_row, cv = i % per_row, j = j0 + r;
+        raw[u] = (i < total && j <= jmax) ? *reinterpret_cast<const uint4*>(src + (size_t)j * ld + cv * VN) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i >= total) break;
+        float* d = dst + (i / per_row) * pitch + (i % per_row) * VN;
+        if constexpr (sizeof(T) == 2) {                      // zero bits are 0.0f in both types
+          *reinterpret_cast<float4*>(d) = make_float4(bf16_lo(raw[u].x), bf16_hi(raw[u].x), bf16_lo(raw[u].y), bf16_hi(raw[u].y));
+          *reinterpret_cast<float4*>(d + 4) = make_float4(bf16_lo(raw[u].z), bf16_hi(raw[u].z), bf16_lo(raw[u].w), bf16_hi(raw[u].w));
+        } else {
+          *reinterpret_cast<uint4*>(d) = raw[u];
+        }
       }
     }
     return;
@@ -252,8 +270,8 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, 
     const int r = i / DP, c = i % DP, s = q0 + r;
     Qs[i] = (s < p.S && c < p.D) ? to_f(q[((size_t)(b * p.S + s) * p.H + h) * p.D + c]) : 0.0f;
   }
-  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.ldk;
-  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.ldv;
+  const T* kbase = kc + (size_t)b * p.k_bs + (size_t)g * p.k_hs;
+  const T* vbase = vc + (size_t)b * p.v_bs + (size_t)g * p.v_hs;
   float mrun[AR_QW], lrun[AR_QW], acc[AR_QW][NV];
 #pragma unroll
   for (int qi = 0; qi < AR_QW; ++qi) {
@@ -339,8 +357,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(AttnParams p
   const int hi = p.cache_len ? *p.cache_len : 0;
   int lo = p.pad_left ? p.pad_left[b] : 0;
   if (p.window > 0) lo = max(lo, hi - p.window + 1);
-  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.ldk;
-  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.ldv;
+  const T* kbase = kc + (size_t)b * p.k_bs + (size_t)g * p.k_hs;
+  const T* vbase = vc + (size_t)b * p.v_bs + (size_t)g * p.v_hs;
   float mrun = -INFINITY, lrun = 0.0f, acc[AT_MAXV] = {};
   for (int j0 = (lo & ~31) + 32 * warp; j0 <= hi; j0 += 32 * AD_WARPS)
     attn_block<T>(qs, kbase, vbase, j0, lo, hi, p.D, p.Dv, p.ldk, p.ldv, p.scale, mrun, lrun, acc);
@@ -392,8 +410,8 @@ __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p,
     const int r = i / DP, c = i % DP;
     Qs[i] = c < p.D ? to_f(q[((size_t)b * p.H + g * R + r) * p.D + c]) : 0.0f;
   }
-  const T* kbase = kc + ((size_t)b * p.G + g) * p.T * p.ldk;
-  const T* vbase = vc + ((size_t)b * p.G + g) * p.T * p.ldv;
+  const T* kbase = kc + (size_t)b * p.k_bs + (size_t)g * p.k_hs;
+  const T* vbase = vc + (size_t)b * p.v_bs + (size_t)g * p.v_hs;
   float mrun[AS_RW], lrun[AS_RW], acc[AS_RW][NV];
 #pragma unroll
   for (int qi = 0; qi < AS_RW; ++qi) {
@@ -518,7 +536,7 @@ extern "C" JL_API int jl_attn_prep(const float* y, int ldy, int q_off, int k_off
 extern "C" JL_API int jl_attn_generic_splits(int B, int H, int G, int T_cap) {
   if (G <= 0 || H / G > AS_WARPS * AS_RW) return 0;      // wider groups: the one-CTA-per-head kernel
   int s = 296 / (B * G > 0 ? B * G : 1);                 // about one resident wave of CTAs
-  const int tiles = (T_cap + 63) / 64;                   // at least two key tiles per split at full capacity
+  const int tiles = (T_cap + 31) / 32;                   // a split is at least one 32-key tile at full capacity
   if (s > tiles) s = tiles;
   if (s > 64) s = 64;
   return s < 1 ? 1 : s;
@@ -526,11 +544,14 @@ extern "C" JL_API int jl_attn_generic_splits(int B, int H, int G, int T_cap) {
 
 static int attn_launch(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
                        const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk,
-                       int ldv, int window, float scale, float* scratch, int splits, int dtype, void* stream) {
+                       int ldv, int window, float scale, float* scratch, int splits, int dtype, void* stream,
+                       long long k_bs = 0, long long k_hs = 0, long long v_bs = 0, long long v_hs = 0) {
   JL_CHECK_ARG(B >= 1 && S >= 1 && G >= 1 && H % G == 0, "jl_attn_generic: H=%d not a multiple of G=%d", H, G);
   JL_CHECK_ARG(Dv <= 32 * AT_MAXV, "jl_attn_generic: value size %d above %d", Dv, 32 * AT_MAXV);
   JL_CHECK_ARG(ldk >= D && ldv >= Dv && window >= 0, "jl_attn_generic: bad pitch %d / %d or window %d", ldk, ldv, window);
-  AttnParams p{B, S, H, G, D, Dv, T_cap, ldk, ldv, window, scale, cache_len, pad_left, gate, ldg};
+  if (k_bs == 0 && k_hs == 0) { k_hs = (long long)T_cap * ldk; k_bs = k_hs * G; }
+  if (v_bs == 0 && v_hs == 0) { v_hs = (long long)T_cap * ldv; v_bs = v_hs * G; }
+  AttnParams p{B, S, H, G, D, Dv, T_cap, ldk, ldv, k_bs, k_hs, v_bs, v_hs, window, scale, cache_len, pad_left, gate, ldg};
   cudaStream_t st = (cudaStream_t)stream;
   if (S == 1 && scratch != nullptr && splits >= 1 && H / G <= AS_WARPS * AS_RW) {
     const int dp = ((D + 3) & ~3) + 4;
@@ -580,20 +601,22 @@ extern "C" JL_API int jl_attn_generic(const void* q, const void* k_cache, const 
 
 extern "C" JL_API int jl_attn_windowed(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cache_len,
                                        const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk, int ldv,
-                                       int window, float scale, float* scratch, int splits, int dtype, void* stream) {
+                                       long long k_bs, long long k_hs, long long v_bs, long long v_hs, int window, float scale,
+                                       float* scratch, int splits, int dtype, void* stream) {
   return attn_launch(q, k_cache, v_cache, out, nullptr, 0, cache_len, pad_left, B, S, H, G, D, Dv, T_cap, ldk, ldv, window, scale,
-                     scratch, splits, dtype, stream);
+                     scratch, splits, dtype, stream, k_bs, k_hs, v_bs, v_hs);
 }
 
 extern "C" JL_API int jl_latent_prep(const float* y, int ldy, int q_off, int q_rank, int kv_off, int kv_rank, int rot_dim, int rot,
                                      int layout, const void* wq_norm, const void* wkv_norm, void* cq, void* cache,
                                      const float* cos_t, const float* sin_t, int max_pos, float eps, const int* cache_len,
-                                     const int* pad_left, int B, int S, int T_cap, int dtype, void* stream) {
+                                     const int* pad_left, int B, int S, int T_cap, void* c_out, void* kr_out, int dtype,
+                                     void* stream) {
   JL_CHECK_ARG(B >= 1 && S >= 1 && q_rank >= 0 && kv_rank >= 1 && rot_dim >= 0, "jl_latent_prep: bad shape");
   JL_CHECK_ARG(rot >= 0 && rot <= rot_dim && rot % 2 == 0, "jl_latent_prep: rot=%d must be even and <= rot_dim=%d", rot, rot_dim);
   JL_CHECK_ARG(layout == 0 || layout == 1, "jl_latent_prep: layout %d", layout);
   LatentPrepParams p{y, ldy, q_off, q_rank, kv_off, kv_rank, rot_dim, rot, layout, cos_t, sin_t, max_pos, eps, B, S, T_cap,
-                     cache_len, pad_left};
+                     cache_len, pad_left, c_out, kr_out};
   JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(latent_prep_kernel<T>, dim3(B * S), dim3(128), 0, (cudaStream_t)stream, p, (const T*)wq_norm,
                                          (const T*)wkv_norm, (T*)cq, (T*)cache));
   JL_CUDA(cudaGetLastError());

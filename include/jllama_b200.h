@@ -323,19 +323,22 @@ int jl_linear_tile_rows(void);
 int jl_linear_grouped(const void* x, int ldx, long long x_bs, const void* w, long long w_bs, void* out, int ldo, long long o_bs,
                       int nbatch, int x_div, int M, int N, int K, int act, float p0, float p1, const int* w_index,
                       const int* tile_group, const int* row_src, int dtype, int out_f32, void* stream);
-/* jl_attn_generic with cache row pitches ldk / ldv (keys and values may be columns of one cached row) and a sliding window:
- * window > 0: a query at slot i sees slots i - window + 1 .. i only. */
+/* jl_attn_generic with cache row pitches ldk / ldv (keys and values may be columns of one cached row), batch-row and head
+ * strides in elements (all four 0: the [B][G][T_cap][ld] cache layout; token-major projections [B*T][G][d] have bs = T*G*d,
+ * hs = d, ld = G*d) and a sliding window: window > 0: a query at slot i sees slots i - window + 1 .. i only. */
 int jl_attn_windowed(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cache_len,
-                     const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk, int ldv, int window,
-                     float scale, float* scratch, int splits, int dtype, void* stream);
+                     const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk, int ldv,
+                     long long k_bs, long long k_hs, long long v_bs, long long v_hs, int window, float scale, float* scratch,
+                     int splits, int dtype, void* stream);
 /* Latent attention, preparation.  y fp32 [B*S, ldy] holds the query latent (q_rank columns at q_off; 0: none) and the key /
  * value latent followed by the rotated key part shared by the heads (kv_rank + rot_dim columns at kv_off).  The latents are
  * RMS-normed with plain weights; the key part is rotated on its first `rot` channels.  cq [B*S, q_rank]; cache
- * [B][T_cap][kv_rank + rot_dim], the token's row at slot *cache_len + s. */
+ * [B][T_cap][kv_rank + rot_dim], the token's row at slot *cache_len + s; c_out [B*S, kv_rank] / kr_out [B*S, rot_dim]
+ * (optional): token-major copies of the two parts of the appended row. */
 int jl_latent_prep(const float* y, int ldy, int q_off, int q_rank, int kv_off, int kv_rank, int rot_dim, int rot, int layout,
                    const void* wq_norm, const void* wkv_norm, void* cq, void* cache, const float* cos_t, const float* sin_t,
-                   int max_pos, float eps, const int* cache_len, const int* pad_left, int B, int S, int T_cap, int dtype,
-                   void* stream);
+                   int max_pos, float eps, const int* cache_len, const int* pad_left, int B, int S, int T_cap, void* c_out,
+                   void* kr_out, int dtype, void* stream);
 /* out[m, h, out_off + d] = rotary(in[m, h, in_off + d]), d < n, at the token's position: a slice of every head rotated and
  * copied into another head layout (head pitches in_hs / out_hs, row pitches ldi / ldo). */
 int jl_rotary_slice(const void* in, int ldi, int in_hs, int in_off, void* out, int ldo, int out_hs, int out_off, int H, int n,

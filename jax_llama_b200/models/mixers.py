@@ -181,11 +181,20 @@ class GlaMixer:
 
 class LatentAttentionMixer:
     """Softmax attention through low-rank latents.  Per token the layer keeps one row [normed key/value latent | rotated
-    key part shared by the heads]; nothing per head.  The keys' and values' up-projections are applied on the query
-    side: with q_h = [a_h | r_h] (unrotated | rotated) the score a_h · (U_h c) + r_h · k_rot equals (U_hᵀ a_h) · c +
-    r_h · k_rot, and Σ p_j (V_h c_j) = V_h (Σ p_j c_j) — so the attention itself runs over the cached rows with one
-    shared key/value head of width kv_rank + rot_dim (keys) and kv_rank (values), in the windowed generic kernel, and
-    two per-head batched products map into and out of the latent."""
+    key part shared by the heads]; nothing per head.
+
+    One token at a time (and prompt portions that continue a cache) the keys' and values' up-projections are applied on
+    the query side: with q_h = [r_h | a_h] (rotated | unrotated) the score a_h · (U_h c) + r_h · k_rot equals
+    (U_hᵀ a_h) · c + r_h · k_rot, and Σ p_j (V_h c_j) = V_h (Σ p_j c_j) — so the attention runs over the cached rows with
+    one shared key/value head of width kv_rank + rot_dim (keys) and kv_rank (values), and two per-head batched products
+    map into and out of the latent: every cached row is read once for all heads.
+
+    A prompt that starts a sequence projects its latents up instead (two tensor-core GEMMs for all heads) and attends
+    with per-head keys [k_rot | U_h c] and values V_h c in token-major layout, which costs a third of the arithmetic of
+    the latent-space form at these head sizes.  Both forms run the windowed generic attention kernel.
+
+    Internally a query head is laid out [rot_dim rotated | dim unrotated] (the rows of the query up-projection are
+    permuted once at load), so that the rotation applies to the leading channels of a head as in the other mixers."""
 
     kind = "latent_attention"
 
@@ -195,14 +204,18 @@ class LatentAttentionMixer:
         self.w_in, offs = _stack_rows([w["dq"], w["dkv"]])
         self.q_off, self.kv_off = offs
         self.q_norm, self.kv_norm = w["dq.norm"].contiguous(), w["dkv.norm"].contiguous()
-        self.uq = w["uq"].contiguous()                                           # [H·(dim + rot_dim), q_rank]
+        uq = w["uq"].view(s.heads, s.dim + s.rot_dim, s.q_rank)                 # stored [dim unrotated | rot_dim rotated]
+        self.uq = torch.cat([uq[:, s.dim:], uq[:, :s.dim]], 1).reshape(s.heads * (s.dim + s.rot_dim), s.q_rank).contiguous()
         self.uk_t = w["uk"].view(s.heads, s.dim, s.kv_rank).transpose(1, 2).contiguous()    # [H, kv_rank, dim]
         self.uv = w["uv"].view(s.heads, s.vdim, s.kv_rank).contiguous()          # [H, vdim, kv_rank]
+        self.w_kv, kv_offs = _stack_rows([w["uk"], w["uv"]])                     # [H·dim | H·vdim, kv_rank]: prompts
+        self.v_col = kv_offs[1]
         self.wo = w["o"].contiguous()
         self.dtype = self.wo.dtype
         self.row = s.kv_rank + s.rot_dim
 
     def weights(self) -> List[torch.Tensor]:
+        """What a decode step streams (the stacked up-projection of prompts holds the same values once more)."""
         return [self.w_in, self.q_norm, self.kv_norm, self.uq, self.uk_t, self.uv, self.wo]
 
     def new_cache(self, batch: int, length: int, device: torch.device) -> Tuple[torch.Tensor, None]:
@@ -218,20 +231,42 @@ class LatentAttentionMixer:
         rot = s.rot.dims if s.rot is not None else 0
         layout = SK.ROT_LAYOUTS[s.rot.layout] if s.rot is not None else 0
         kc = cache.ks[layer]                                                   # [B, T, kv_rank + rot_dim]
+        starts = S > 1 and int(cache.index) == 0                               # a prompt from an empty cache
         y = SK.linear(h, self.w_in)                                            # fp32 [M, query latent | kv latent | key part]
-        cq = SK.latent_prep(y, self.q_off, s.q_rank, self.kv_off, s.kv_rank, s.rot_dim, rot, layout, self.q_norm,
-                            self.kv_norm, kc, rope[0], rope[1], self.eps, cache.len_dev, cache.pad_left, B, S)
-        q = SK.linear(cq, self.uq, out_f32=False)                              # [M, H·(dim + rot_dim)]
+        cq, c_new, kr_new = SK.latent_prep(y, self.q_off, s.q_rank, self.kv_off, s.kv_rank, s.rot_dim, rot, layout,
+                                           self.q_norm, self.kv_norm, kc, rope[0], rope[1], self.eps, cache.len_dev,
+                                           cache.pad_left, B, S, token_major=starts)
+        q = SK.linear(cq, self.uq, out_f32=False)                              # [M, H·(rot_dim + dim)]
+        if starts:
+            return self._attend_projected(q, c_new, kr_new, cache, B, S, rot, layout, rope)
         qa = torch.empty((M, H * self.row), dtype=self.dtype, device=h.device)
-        SK.linear_batched(q, self.uk_t, qa, nbatch=H, rows=M, x_bs=qd, o_bs=self.row)      # U_hᵀ a_h
+        a = q[:, s.rot_dim:] if s.rot_dim else q                               # head h's unrotated part starts at h·qd
+        SK.linear_batched(a, self.uk_t, qa, nbatch=H, rows=M, x_bs=qd, o_bs=self.row)      # U_hᵀ a_h
         if s.rot_dim:
-            SK.rotary_slice(q, qd, s.dim, qa, self.row, s.kv_rank, H, s.rot_dim, rot, layout, rope[0], rope[1],
+            SK.rotary_slice(q, qd, 0, qa, self.row, s.kv_rank, H, s.rot_dim, rot, layout, rope[0], rope[1],
                             cache.len_dev, cache.pad_left, B, S)
         ctx = SK.attn_windowed(qa, kc, kc, cache.len_dev, cache.pad_left, B, S, H, 1, self.row, s.kv_rank, kc.shape[1],
                                self.row, self.row, s.window, s.scale)         # [M, H·kv_rank]
         out = torch.empty((M, H * s.vdim), dtype=self.dtype, device=h.device)
         SK.linear_batched(ctx, self.uv, out, nbatch=H, rows=M, x_bs=s.kv_rank, o_bs=s.vdim)
         return out
+
+    def _attend_projected(self, q: torch.Tensor, c_new: torch.Tensor, kr_new: torch.Tensor, cache: "object", B: int, S: int,
+                          rot: int, layout: int, rope: Tuple[torch.Tensor, torch.Tensor]) -> torch.Tensor:
+        """Per-head keys and values of the S new tokens of every row, token-major; slot == index within the prompt."""
+        s = self.spec
+        M, H, qd = B * S, s.heads, s.dim + s.rot_dim
+        kv = SK.linear(c_new, self.w_kv, out_f32=False)                        # [M, H·dim | H·vdim (| padding)]
+        qf = torch.empty_like(q)
+        SK.rotary_slice(q, qd, 0, qf, qd, 0, H, qd, rot, layout, rope[0], rope[1], cache.len_dev, cache.pad_left, B, S)
+        kf = torch.empty((M, H * qd), dtype=self.dtype, device=q.device)       # [M, H, rot_dim | dim]
+        if s.rot_dim:
+            SK.rotary_slice(kr_new, 0, 0, kf, qd, 0, H, s.rot_dim, 0, 0, rope[0], rope[1], cache.len_dev, cache.pad_left, B, S)
+        SK.rotary_slice(kv, s.dim, 0, kf, qd, s.rot_dim, H, s.dim, 0, 0, rope[0], rope[1], cache.len_dev, cache.pad_left, B, S)
+        v = kv[:, self.v_col:]
+        ldv = kv.stride(0)
+        return SK.attn_windowed(qf, kf, v, cache.len_dev, cache.pad_left, B, S, H, H, qd, s.vdim, S, H * qd, ldv, s.window,
+                                s.scale, strides=(S * H * qd, qd, S * ldv, s.vdim))
 
 
 class RetentionMixer:

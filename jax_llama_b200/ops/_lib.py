@@ -73,8 +73,8 @@ _HYBRID = {
     "jl_linear_tile_rows": (i32, []),
     "jl_linear_grouped": (i32, [vp, i32, i64, vp, i64, vp, i32, i64, i32, i32, i32, i32, i32, i32, f32, f32, ip, ip, ip, i32, i32,
                                 vp]),
-    "jl_attn_windowed": (i32, [vp, vp, vp, vp, ip, ip] + [i32] * 10 + [f32, fp, i32, i32, vp]),
-    "jl_latent_prep": (i32, [fp] + [i32] * 8 + [vp, vp, vp, vp, fp, fp, i32, f32, ip, ip, i32, i32, i32, i32, vp]),
+    "jl_attn_windowed": (i32, [vp, vp, vp, vp, ip, ip] + [i32] * 9 + [i64] * 4 + [i32, f32, fp, i32, i32, vp]),
+    "jl_latent_prep": (i32, [fp] + [i32] * 8 + [vp, vp, vp, vp, fp, fp, i32, f32, ip, ip, i32, i32, i32, vp, vp, i32, vp]),
     "jl_rotary_slice": (i32, [vp, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, fp, fp, i32, ip, ip, i32, i32, i32, vp]),
     "jl_moe_route": (i32, [fp] + [i32] * 9 + [f32, ip, fp, vp]),
     "jl_moe_sorted_rows": (i32, [i32, i32, i32]),

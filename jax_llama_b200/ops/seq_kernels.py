@@ -260,17 +260,21 @@ def linear_sorted(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_grou
 
 def latent_prep(y: torch.Tensor, q_off: int, q_rank: int, kv_off: int, kv_rank: int, rot_dim: int, rot: int, layout: int,
                 wq_norm: Optional[torch.Tensor], wkv_norm: torch.Tensor, cache: torch.Tensor, cos: torch.Tensor,
-                sin: torch.Tensor, eps: float, cache_len: torch.Tensor, pad_left: Optional[torch.Tensor], B: int, S: int
-                ) -> Optional[torch.Tensor]:
-    """Norm both latents, rotate the shared key part, append [latent | key part] to cache [B, T, kv_rank + rot_dim];
-    returns the normed query latent [B·S, q_rank] (None when q_rank == 0)."""
+                sin: torch.Tensor, eps: float, cache_len: torch.Tensor, pad_left: Optional[torch.Tensor], B: int, S: int,
+                token_major: bool = False) -> "tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor]]":
+    """Norm both latents, rotate the shared key part, append [latent | key part] to cache [B, T, kv_rank + rot_dim].
+    Returns (normed query latent [B·S, q_rank] or None when q_rank == 0, and with `token_major` contiguous copies of
+    the appended latents [B·S, kv_rank] and key parts [B·S, rot_dim], else None, None)."""
     _need(y, torch.float32, "y")
-    cq = torch.empty((B * S, q_rank), dtype=cache.dtype, device=y.device) if q_rank else None
+    M = B * S
+    cq = torch.empty((M, q_rank), dtype=cache.dtype, device=y.device) if q_rank else None
+    c_out = torch.empty((M, kv_rank), dtype=cache.dtype, device=y.device) if token_major else None
+    kr_out = torch.empty((M, max(rot_dim, 1)), dtype=cache.dtype, device=y.device) if token_major else None
     _lib.check(_lib.lib().jl_latent_prep(
         y.data_ptr(), y.stride(0), q_off, q_rank, kv_off, kv_rank, rot_dim, rot, layout, _p(wq_norm), wkv_norm.data_ptr(),
         _p(cq), cache.data_ptr(), cos.data_ptr(), sin.data_ptr(), cos.shape[0], float(eps), _p(cache_len), _p(pad_left), B, S,
-        cache.shape[1], dtype_code(cache.dtype), _stream()), "jl_latent_prep")
-    return cq
+        cache.shape[1], _p(c_out), _p(kr_out), dtype_code(cache.dtype), _stream()), "jl_latent_prep")
+    return cq, c_out, kr_out
 
 
 def rotary_slice(src: torch.Tensor, in_hs: int, in_off: int, out: torch.Tensor, out_hs: int, out_off: int, H: int, n: int,
@@ -286,9 +290,12 @@ def rotary_slice(src: torch.Tensor, in_hs: int, in_off: int, out: torch.Tensor, 
 
 def attn_windowed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_len: torch.Tensor,
                   pad_left: Optional[torch.Tensor], B: int, S: int, H: int, G: int, D: int, Dv: int, T_cap: int, ldk: int,
-                  ldv: int, window: int, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Causal attention of S new tokens per row over cache rows of pitch ldk / ldv (keys and values may be columns of
-    one cached row; caches [B, G, T_cap, ·]); window > 0 keeps the last `window` slots up to the query's own."""
+                  ldv: int, window: int, scale: float, out: Optional[torch.Tensor] = None,
+                  strides: "tuple[int, int, int, int]" = (0, 0, 0, 0)) -> torch.Tensor:
+    """Causal attention of S new tokens per row over key / value rows of pitch ldk / ldv (keys and values may be
+    columns of one cached row); window > 0 keeps the last `window` slots up to the query's own.  `strides`: elements
+    between batch rows and between key/value heads for keys and for values — all zero: caches [B, G, T_cap, ·];
+    token-major projections [B·T, G, d] have (T·G·d, d) and a row pitch of G·d."""
     if out is None:
         out = torch.empty((B * S, H * Dv), dtype=q.dtype, device=q.device)
     L = _lib.lib()
@@ -299,7 +306,8 @@ def attn_windowed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
             scratch = torch.empty(B * H * splits * (Dv + 2), dtype=torch.float32, device=q.device)
     _lib.check(L.jl_attn_windowed(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(cache_len), _p(pad_left), B, S, H, G, D, Dv,
-        T_cap, ldk, ldv, int(window), float(scale), _p(scratch), splits, dtype_code(q.dtype), _stream()), "jl_attn_windowed")
+        T_cap, ldk, ldv, *(int(v) for v in strides), int(window), float(scale), _p(scratch), splits, dtype_code(q.dtype),
+        _stream()), "jl_attn_windowed")
     return out
 
 

@@ -267,3 +267,242 @@ def run(sizes: List[str], prompt_len: int = 2048, steps: int = 64, warmup: int =
             entry["kernels"] = _kernel_table(s, dev, peaks, prompt_len)
         result["sizes"][name] = entry
     return result
+
+
+# --------------------------------------------------------------------------- Nikonex beside Folirax
+# width, heads, dense ff of the Folirax model; the Nikonex model of equal size has top x expert_ff + shared_ff = ff active
+# feed-forward columns per token, the same head counts and recurrent head sizes, and latent attention with 128 + 64
+# wide heads over a latent of 512
+NIKONEX_SIZES: Dict[str, Dict[str, int]] = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, ff=8192, layers=8, vocab=32000, experts=32, top=4, expert_ff=1536,
+                  shared_ff=2048, q_rank=768, kv_rank=512, window=1024),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, ff=14336, layers=4, vocab=32000, experts=32, top=4, expert_ff=2560,
+                  shared_ff=4096, q_rank=1536, kv_rank=512, window=1024),
+}
+
+
+def nikonex_config(s: Dict[str, int]) -> Any:
+    from ..config import NikonexConfig
+
+    H = s["heads"]
+    lat = {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": s["q_rank"], "kv_rank": s["kv_rank"],
+           "scale": 192 ** -0.5, "mask": {"size": s["window"]},
+           "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    ret = {"heads": H, "dim": 64, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(H - 1, 1)) for h in range(H)],
+           "rot": {"dims": 64, "base": 10000.0}}
+    mlp = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "shared": {"ff": s["shared_ff"]},
+           "router": {"experts": s["experts"], "top": s["top"], "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
+    block = [("retention", ret, None), ("latent_attention", lat, mlp), ("latent_attention", lat, mlp), ("retention", ret, mlp)]
+    layers = [{"type": block[i % 4][0], "mixer": block[i % 4][1], "mlp": block[i % 4][2]} for i in range(s["layers"])]
+    return NikonexConfig.from_dict({"architecture": "Nikonex", "vocab": s["vocab"], "width": s["width"],
+                                    "norm": {"eps": 1e-5}, "residual_mult": 0.5, "layers": layers})
+
+
+def _nikonex_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str, float], prompt_len: int) -> List[Dict[str, Any]]:
+    """Each kernel that Nikonex adds, at this size, beside the like kernel of the Folirax path: ms, achieved rate and the
+    fraction of the measured roofline, and how much farther from it the new kernel is (`distance_ratio`)."""
+    from ..config import MoeMlpSpec
+    from ..models.feedforward import MoeFeedForward
+    from ..models.mixers import rotary_table
+    from ..ops import seq_kernels as SK
+
+    t = Timer(dev)
+    hbm, tf = peaks["hbm_gbs"], peaks["bf16_tflops"]
+    W, H, F = s["width"], s["heads"], s["ff"]
+    E, top, ef, sf = s["experts"], s["top"], s["expert_ff"], s["shared_ff"]
+    rank, qr, win = s["kv_rank"], s["q_rank"], s["window"]
+    D, R, Dv, gd, gv = 128, 64, 128, 64, 128
+    P = prompt_len
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    rows: List[Dict[str, Any]] = []
+
+    def add(name: str, ms: float, like: str, like_ms: float, nbytes: float = 0.0, flops: float = 0.0, like_nbytes: float = 0.0,
+            like_flops: float = 0.0, note: str = "") -> None:
+        r: Dict[str, Any] = {"kernel": name, "ms": round(ms, 4), "like": like, "like_ms": round(like_ms, 4) if like_ms else None}
+        frac = like_frac = None
+        if nbytes:
+            r["gbs"] = round(nbytes / ms / 1e6, 1)
+            frac = nbytes / ms / 1e6 / hbm
+            r["frac_hbm_of_measured"] = round(frac, 3)
+            if like_ms:
+                like_frac = (like_nbytes or nbytes) / like_ms / 1e6 / hbm
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            frac = flops / ms / 1e9 / tf
+            r["frac_bf16_of_measured"] = round(frac, 4)
+            if like_ms:
+                like_frac = (like_flops or flops) / like_ms / 1e9 / tf
+        if like_frac is not None:
+            r["like_frac"] = round(like_frac, 4)
+            r["distance_ratio"] = round(like_frac / frac, 2)
+        if note:
+            r["note"] = note
+        rows.append(r)
+
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    pad = torch.zeros(1, dtype=torch.int32, device=dev)
+    ctx_len = torch.full((1,), P, dtype=torch.int32, device=dev)
+
+    # ---- residual step: both branches + two norms in one kernel / one branch + post-norm + next norm
+    x, y1, y2 = (torch.randn(P, W, device=dev) for _ in range(3))
+    w1, w2 = torch.ones(W, **bf), torch.ones(W, **bf)
+    add("branch_add_norm (two branches, two norms)", t.kernel(lambda: SK.branch_add_norm(x, y1, y2, 0.5, w1, w2, 1e-5)),
+        "postnorm_add (+ next norm)", t.kernel(lambda: SK.postnorm_add(y1, w1, x, 1e-5, 1.0, w_next=w2)),
+        nbytes=P * W * 20.0, like_nbytes=P * W * 14.0)
+
+    # ---- latent attention: preparation, windowed attention over the cached latents (prompt, one token)
+    T = P + 8
+    cos, sin = rotary_table(R, 10000.0, T, dev)
+    n_in = qr + rank + R
+    y = torch.randn(P, n_in, device=dev)
+    wqn, wkn = torch.ones(qr, **bf), torch.ones(rank, **bf)
+    cache = torch.zeros(1, T, rank + R, **bf)
+    prep = lambda: SK.latent_prep(y, 0, qr, qr, rank, R, R, 0, wqn, wkn, cache, cos, sin, 1e-5, zero, pad, 1, P)   # noqa: E731
+    prep()
+    yq = torch.randn(P, (H + 2 * H // 4) * D + 8, device=dev)
+    qo = torch.empty(P, H * D, **bf)
+    kc, vc = torch.zeros(1, H // 4, T, D, **bf), torch.zeros(1, H // 4, T, Dv, **bf)
+    add("latent_prep (two norms, rotation, append)", t.kernel(prep), "attn_prep (rotation, unit norm, append)",
+        t.kernel(lambda: SK.attn_prep(yq, 0, H * D, (H + H // 4) * D, qo, kc, vc, cos, sin, 64, True, 1e-5, zero, pad, 1, P, H,
+                                      H // 4, D, Dv)),
+        nbytes=P * n_in * 4.0 + P * (qr + rank + R) * 2.0, like_nbytes=P * (H + 2 * H // 4) * D * 6.0)
+    row = rank + R
+    qa = torch.randn(P, H * row, **bf) * 0.05
+    win_keys = sum(min(i + 1, win) for i in range(P))
+    fl = 2.0 * H * win_keys * (row + rank)
+    q128 = torch.randn(P, H * D, **bf) * 0.05
+    kg, vg = torch.randn(1, H // 4, T, D, **bf), torch.randn(1, H // 4, T, Dv, **bf)
+    full_keys = P * (P + 1) / 2
+    add("attn_rows_kernel, windowed, shared latent rows (prompt)",
+        t.kernel(lambda: SK.attn_windowed(qa, cache, cache, zero, pad, 1, P, H, 1, row, rank, T, row, row, win, 192 ** -0.5), reps=3),
+        "attn_rows_kernel (prompt)", t.kernel(lambda: SK.attn_generic(q128, kg, vg, None, zero, pad, 1, P, H, D ** -0.5), reps=3),
+        flops=fl, like_flops=2.0 * H * full_keys * (D + Dv), note="the same SIMT kernel; fractions are of the tensor-core peak")
+    q1 = torch.randn(1, H * row, **bf) * 0.05
+    q1g = torch.randn(1, H * D, **bf) * 0.05
+    add("attn_split_kernel, windowed, shared latent rows (one token)",
+        t.kernel(lambda: SK.attn_windowed(q1, cache, cache, ctx_len, pad, 1, 1, H, 1, row, rank, T, row, row, win, 192 ** -0.5)),
+        "attn_split_kernel (one token)", t.kernel(lambda: SK.attn_generic(q1g, kg, vg, None, ctx_len, pad, 1, 1, H, D ** -0.5)),
+        nbytes=min(win, P) * row * 2.0, like_nbytes=2.0 * (H // 4) * P * D * 2.0,
+        note="reads one shared latent row per key for all heads")
+    # per-head products into and out of the latent
+    qh = torch.randn(P, H * (D + R), **bf) * 0.05
+    ukt = torch.randn(H, rank, D, **bf) * 0.05
+    qabs = torch.empty(P, H * row, **bf)
+    wd = torch.randn(H * D, W, **bf) * 0.02
+    xp = torch.randn(P, W, **bf)
+    add("linear_batched (per-head map into the latent, prompt)",
+        t.kernel(lambda: SK.linear_batched(qh, ukt, qabs, nbatch=H, rows=P, x_bs=D + R, o_bs=row), reps=3),
+        "tcgen05 GEMM (q projection)", t.kernel(lambda: SK.linear(xp, wd, out_f32=False)),
+        flops=2.0 * P * H * D * rank, like_flops=2.0 * P * H * D * W,
+        note="SIMT tiles: the tensor-core GEMM takes one weight matrix per launch or per 128-row tile, not per column slice")
+    q1h = torch.randn(1, H * (D + R), **bf)
+    q1abs = torch.empty(1, H * row, **bf)
+    x1 = torch.randn(1, W, **bf)
+    add("linear_batched (per-head map into the latent, one token)",
+        t.kernel(lambda: SK.linear_batched(q1h, ukt, q1abs, nbatch=H, rows=1, x_bs=D + R, o_bs=row)),
+        "linear_rows (q projection, one token)", t.kernel(lambda: SK.linear(x1, wd)),
+        nbytes=ukt.numel() * 2.0, like_nbytes=wd.numel() * 2.0)
+
+    # ---- retention beside gated linear attention
+    n_y = 2 * H * gd + 2 * H * gv + 16
+    yg = torch.randn(P, n_y, device=dev) * 0.3
+    a2 = torch.randn(H * gd, 16, **bf) * 0.1
+    a2b = torch.full((H * gd,), 3.0, **bf)
+    state = torch.zeros(1, H, gd, gv, device=dev)
+    decay = torch.linspace(0.97, 0.999, H, device=dev)
+    rc, rs = rotary_table(gd, 10000.0, T, dev)
+    rec = 3.0 * P * H * gd * gv
+    ms_r = t.kernel(lambda: SK.retention_scan(yg, 0, H * gd, 2 * H * gd, decay, rc, rs, gd, SK.ROT_HALF, gd ** -0.5, state, zero, pad,
+                                              1, P, H, gd, gv), reps=5)
+    ms_g = t.kernel(lambda: SK.gla_scan(yg, 0, H * gd, 2 * H * gd, 2 * H * gd + 2 * H * gv, a2, a2b, state, zero, pad, 1, P, H, gd,
+                                        gv, gd ** -0.5, 16.0), reps=5)
+    rows.append({"kernel": "retention scan (prompt)", "ms": round(ms_r, 4), "like": "gla scan (prompt)", "like_ms": round(ms_g, 4),
+                 "recurrence_tflops_fp32": round(rec / ms_r / 1e9, 2), "like_recurrence_tflops_fp32": round(rec / ms_g / 1e9, 2),
+                 "distance_ratio": round(ms_r / ms_g, 2), "note": "the same kernels; the decay is a constant per head"})
+    state8 = torch.zeros(8, H, gd, gv, device=dev)
+    yg8 = yg[:8].contiguous()
+    pad8 = torch.zeros(8, dtype=torch.int32, device=dev)
+    add("retention scan (one token, batch 8)",
+        t.kernel(lambda: SK.retention_scan(yg8, 0, H * gd, 2 * H * gd, decay, rc, rs, gd, SK.ROT_HALF, gd ** -0.5, state8, ctx_len,
+                                           pad8, 8, 1, H, gd, gv)),
+        "gla scan (one token, batch 8)",
+        t.kernel(lambda: SK.gla_scan(yg8, 0, H * gd, 2 * H * gd, 2 * H * gd + 2 * H * gv, a2, a2b, state8, ctx_len, pad8, 8, 1, H, gd,
+                                     gv, gd ** -0.5, 16.0)), nbytes=2.0 * state8.numel() * 4)
+
+    # ---- mixture of experts beside the dense feed-forward of equal active size
+    spec = MoeMlpSpec(experts=E, top=top, ff=ef, groups=4, keep=2, scale=2.0, shared_ff=0)
+    g = torch.Generator(device=dev).manual_seed(3)
+    wts = {n: (torch.randn(sh, device=dev, generator=g) / sh[1] ** 0.5).to(torch.bfloat16)
+           for n, sh in MoeFeedForward.shapes(spec, W).items()}
+    moe = MoeFeedForward(spec, wts)
+    del wts
+    hp = torch.randn(P, W, device=dev, generator=g).to(torch.bfloat16)
+    z = SK.linear(hp, moe.w_route)
+    route = lambda: SK.moe_route(z, E, top, 4, 2, 2, SK.SCORE_SIGMOID, True, 2.0)      # noqa: E731
+    idx, wt = route()
+    rows.append({"kernel": "moe_route (prompt)", "ms": round(t.kernel(route), 4), "like": "(none)", "like_ms": None,
+                 "note": "one warp per token over the fp32 logits"})
+    sort = lambda: SK.moe_sort(idx, E, tile=SK.GEMM_TILE_ROWS)                            # noqa: E731
+    pos, row_src, tile_group = sort()
+    rows.append({"kernel": "moe_sort (prompt)", "ms": round(t.kernel(sort), 4), "like": "(none)", "like_ms": None,
+                 "note": "one CTA orders the (token, choice) pairs by expert"})
+    nrows = row_src.shape[0]
+    xs = SK.moe_gather(hp, row_src)
+    add("moe_gather (rows in sorted order)", t.kernel(lambda: SK.moe_gather(hp, row_src)), "(none)", 0.0, nbytes=nrows * W * 4.0)
+    wu = torch.randn(top * ef, W, **bf) * 0.02
+    fl_up = 2.0 * P * top * ef * W
+    add("grouped tcgen05 GEMM + relu^2 pass (experts up)",
+        t.kernel(lambda: SK.gemm_grouped(xs, moe.up, tile_group, act=SK.ACT_RELU2, out_f32=False)),
+        "tcgen05 GEMM + relu^2 pass (dense up, equal active size)",
+        t.kernel(lambda: SK.linear(hp, wu, act=SK.ACT_RELU2, out_f32=False)), flops=fl_up,
+        note=f"{nrows} sorted rows for {P * top} pairs (segments rounded up to 128)")
+    tmid = torch.randn(nrows, ef, **bf) * 0.1
+    tdense = torch.randn(P, top * ef, **bf) * 0.1
+    wdn = torch.randn(W, top * ef, **bf) * 0.02
+    add("grouped tcgen05 GEMM, fp32 out (experts down)", t.kernel(lambda: SK.gemm_grouped(tmid, moe.down, tile_group)),
+        "tcgen05 GEMM, fp32 out (dense down, equal active size)", t.kernel(lambda: SK.linear(tdense, wdn)), flops=fl_up)
+    yexp = torch.randn(nrows, W, device=dev)
+    sh = torch.randn(P, W, device=dev)
+    add("moe_combine (weighted sum + gated shared expert)", t.kernel(lambda: SK.moe_combine(yexp, pos, wt, sh, z[:, E:E + 1], W)),
+        "(none)", 0.0, nbytes=P * W * 4.0 * (top + 2))
+    h1 = hp[:1].contiguous()
+    ms_moe1 = t.kernel(lambda: moe.run(h1))
+    wu1 = torch.randn(top * ef, W, **bf) * 0.02
+    wd1 = torch.randn(W, top * ef, **bf) * 0.02
+    t1 = torch.randn(1, top * ef, **bf)
+    ms_dense1 = t.kernel(lambda: SK.linear(t1, wd1)) + t.kernel(lambda: SK.linear(h1, wu1, act=SK.ACT_RELU2, out_f32=False))
+    add("experts, one token (router, choice, two batched weight streams, combine)", ms_moe1,
+        "dense feed-forward of equal active size, one token (two weight streams)", ms_dense1,
+        nbytes=2.0 * top * ef * W * 2 + moe.w_route.numel() * 2.0, like_nbytes=2.0 * top * ef * W * 2,
+        note="five launches against two")
+    return rows
+
+
+def run_nikonex(sizes: List[str], prompt_len: int = 2048, steps: int = 64, warmup: int = 8, batches: List[int] = (1, 8),
+                kernels: bool = True) -> Dict[str, Any]:
+    """Nikonex beside the closest existing design, Folirax, at equal width, depth, head counts and active feed-forward size."""
+    from ..models.hybrid_engine import HybridEngine
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+        peaks = {"hbm_gbs": float(m["hbm_gbs"]), "bf16_tflops": float(m["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        pass
+    result: Dict[str, Any] = {"metric": "nikonex_vs_folirax_equal_size", "data": "synthetic", "dtype": "bf16", "peaks": peaks,
+                              "prompt_len": prompt_len, "steps": steps, "warmup": warmup, "sizes": {}}
+    for name in sizes:
+        s = NIKONEX_SIZES[name]
+        entry: Dict[str, Any] = {"shape": s}
+        for label, cfg in (("nikonex", nikonex_config(s)), ("folirax", folirax_config(s))):
+            eng = HybridEngine.random_init(cfg, dev, seed=0)
+            entry[label] = _model_times(eng, s["vocab"], prompt_len, list(batches), steps, warmup)
+            del eng
+            torch.cuda.empty_cache()
+        if kernels:
+            entry["kernels"] = _nikonex_kernel_table(s, dev, peaks, prompt_len)
+        result["sizes"][name] = entry
+    return result
