@@ -395,23 +395,26 @@ __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p,
   pdl_launch_dependents();
   extern __shared__ float4 smem4[];
   float* smem = reinterpret_cast<float*>(smem4);
-  const int R = p.H / p.G;
+  constexpr int RB = AS_WARPS * AS_RW;                   // query heads a CTA takes; wider groups are cut into blocks of RB
+  const int RG = p.H / p.G, nblk = (RG + RB - 1) / RB;
+  const int g = blockIdx.y / nblk, r0 = (blockIdx.y % nblk) * RB;
+  const int R = min(RB, RG - r0);
   const int DP = ((p.D + 3) & ~3) + 4;
   float* Qs = smem;                                      // [R][DP]
   float* Ks = Qs + R * DP;                               // [32][DP]
-  float* Vs = Ks + 32 * DP;                              // [32][DVP]
-  const int DVP = (p.Dv + 3) & ~3;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int z = blockIdx.x, b = blockIdx.z;
+  const T* kbase = kc + (size_t)b * p.k_bs + (size_t)g * p.k_hs;
+  const T* vbase = vc + (size_t)b * p.v_bs + (size_t)g * p.v_hs;
+  // values that are the leading columns of the key rows (attention over cached latents) are staged once, with the keys
+  const bool v_in_k = vbase == kbase && p.ldv == p.ldk && p.Dv <= p.D;
+  float* Vs = v_in_k ? Ks : Ks + 32 * DP;                // [32][DVP]
+  const int DVP = v_in_k ? DP : (p.Dv + 3) & ~3;
   const int hi = p.cache_len ? *p.cache_len : 0;         // the new token's own slot
   int lo = p.pad_left ? p.pad_left[b] : 0;
   if (p.window > 0) lo = max(lo, hi - p.window + 1);
-  for (int i = threadIdx.x; i < R * DP; i += blockDim.x) {
-    const int r = i / DP, c = i % DP;
-    Qs[i] = c < p.D ? to_f(q[((size_t)b * p.H + g * R + r) * p.D + c]) : 0.0f;
-  }
-  const T* kbase = kc + (size_t)b * p.k_bs + (size_t)g * p.k_hs;
-  const T* vbase = vc + (size_t)b * p.v_bs + (size_t)g * p.v_hs;
+  // the R query rows are consecutive: staged like a key tile (rows beyond R fall into the key buffer, which is filled later)
+  stage_rows<T>(Qs, DP, q + ((size_t)b * p.H + (size_t)g * RG + r0) * p.D, p.D, p.D, 0, R - 1);
   float mrun[AS_RW], lrun[AS_RW], acc[AS_RW][NV];
 #pragma unroll
   for (int qi = 0; qi < AS_RW; ++qi) {
@@ -422,7 +425,7 @@ __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p,
   for (int j0 = (lo & ~31) + 32 * z; j0 <= hi; j0 += 32 * splits) {
     __syncthreads();
     stage_rows<T>(Ks, DP, kbase, p.D, p.ldk, j0, hi);
-    stage_rows<T>(Vs, DVP, vbase, p.Dv, p.ldv, j0, hi);
+    if (!v_in_k) stage_rows<T>(Vs, DVP, vbase, p.Dv, p.ldv, j0, hi);
     __syncthreads();
     const int j = j0 + lane;
     const bool vis = j >= lo && j <= hi;
@@ -465,7 +468,7 @@ __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p,
   for (int qi = 0; qi < AS_RW; ++qi) {
     const int r = warp + AS_WARPS * qi;
     if (r >= R) continue;
-    float* dst = part + (((size_t)b * p.H + g * R + r) * splits + z) * (p.Dv + 2);
+    float* dst = part + (((size_t)b * p.H + (size_t)g * RG + r0 + r) * splits + z) * (p.Dv + 2);
     if (lane == 0) { dst[0] = mrun[qi]; dst[1] = lrun[qi]; }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -479,23 +482,32 @@ template <typename T>
 __global__ void attn_merge_kernel(AttnParams p, const float* __restrict__ part, int splits, T* __restrict__ out) {
   pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
   pdl_launch_dependents();
+  __shared__ float wz[64];                                 // weight of every split (splits <= 64)
+  __shared__ float tot;
   const int h = blockIdx.x, b = blockIdx.y;
   const float* src = part + ((size_t)b * p.H + h) * splits * (p.Dv + 2);
-  float mall = -INFINITY;
-  for (int z = 0; z < splits; ++z) mall = fmaxf(mall, src[(size_t)z * (p.Dv + 2)]);
-  float lall = 0.0f;
-  for (int z = 0; z < splits; ++z) {
-    const float m = src[(size_t)z * (p.Dv + 2)];
-    if (m != -INFINITY) lall += src[(size_t)z * (p.Dv + 2) + 1] * expf(m - mall);
+  if (threadIdx.x < 32) {                                  // the splits' maxima and sums, all loads at once
+    const int lane = threadIdx.x;
+    const float m0 = lane < splits ? src[(size_t)lane * (p.Dv + 2)] : -INFINITY;
+    const float m1 = lane + 32 < splits ? src[(size_t)(lane + 32) * (p.Dv + 2)] : -INFINITY;
+    const float l0 = lane < splits ? src[(size_t)lane * (p.Dv + 2) + 1] : 0.0f;
+    const float l1 = lane + 32 < splits ? src[(size_t)(lane + 32) * (p.Dv + 2) + 1] : 0.0f;
+    const float mall = warp_max(fmaxf(m0, m1));
+    const float w0 = m0 == -INFINITY ? 0.0f : expf(m0 - mall), w1 = m1 == -INFINITY ? 0.0f : expf(m1 - mall);
+    wz[lane] = w0; wz[lane + 32] = w1;
+    float lall = 0.0f;                                     // summed in split order, as the columns below are
+    for (int zz = 0; zz < splits; ++zz)
+      lall += zz < 32 ? __shfl_sync(0xffffffffu, l0 * w0, zz) : __shfl_sync(0xffffffffu, l1 * w1, zz - 32);
+    if (lane == 0) tot = lall;
   }
+  __syncthreads();
+  const float lall = tot;
   float gmul = lall > 0.0f ? 1.0f / lall : 0.0f;
   if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)b * p.ldg + h]);
   for (int c = threadIdx.x; c < p.Dv; c += blockDim.x) {
     float o = 0.0f;
-    for (int z = 0; z < splits; ++z) {
-      const float m = src[(size_t)z * (p.Dv + 2)];
-      if (m != -INFINITY) o += src[(size_t)z * (p.Dv + 2) + 2 + c] * expf(m - mall);
-    }
+#pragma unroll 8
+    for (int zz = 0; zz < splits; ++zz) o = fmaf(src[(size_t)zz * (p.Dv + 2) + 2 + c], wz[zz], o);
     out[((size_t)b * p.H + h) * p.Dv + c] = from_f<T>(o * gmul);
   }
 }
@@ -534,8 +546,9 @@ extern "C" JL_API int jl_attn_prep(const float* y, int ldy, int q_off, int k_off
 }
 
 extern "C" JL_API int jl_attn_generic_splits(int B, int H, int G, int T_cap) {
-  if (G <= 0 || H / G > AS_WARPS * AS_RW) return 0;      // wider groups: the one-CTA-per-head kernel
-  int s = 296 / (B * G > 0 ? B * G : 1);                 // about one resident wave of CTAs
+  if (G <= 0) return 0;
+  const int nblk = (H / G + AS_WARPS * AS_RW - 1) / (AS_WARPS * AS_RW);      // blocks of query heads per key/value head
+  int s = 296 / (B * G * nblk > 0 ? B * G * nblk : 1);   // about one resident wave of CTAs
   const int tiles = (T_cap + 31) / 32;                   // a split is at least one 32-key tile at full capacity
   if (s > tiles) s = tiles;
   if (s > 64) s = 64;
@@ -553,15 +566,16 @@ static int attn_launch(const void* q, const void* k_cache, const void* v_cache, 
   if (v_bs == 0 && v_hs == 0) { v_hs = (long long)T_cap * ldv; v_bs = v_hs * G; }
   AttnParams p{B, S, H, G, D, Dv, T_cap, ldk, ldv, k_bs, k_hs, v_bs, v_hs, window, scale, cache_len, pad_left, gate, ldg};
   cudaStream_t st = (cudaStream_t)stream;
-  if (S == 1 && scratch != nullptr && splits >= 1 && H / G <= AS_WARPS * AS_RW) {
+  if (S == 1 && scratch != nullptr && splits >= 1 && splits <= 64) {
     const int dp = ((D + 3) & ~3) + 4;
-    const size_t smem = (size_t)((H / G + 32) * dp + 32 * ((Dv + 3) & ~3)) * sizeof(float);
+    const int rb = H / G < AS_WARPS * AS_RW ? H / G : AS_WARPS * AS_RW, nblk = (H / G + rb - 1) / rb;
+    const size_t smem = (size_t)((rb + 32) * dp + 32 * ((Dv + 3) & ~3)) * sizeof(float);
     JL_CHECK_ARG(smem <= 200 * 1024, "jl_attn_generic: head sizes %d / %d do not fit the key tile", D, Dv);
 #define JL_AS(NV_)                                                                                                   \
   JL_DISPATCH_DTYPE(dtype, {                                                                                         \
     if (smem > 48 * 1024)                                                                                            \
       JL_CUDA(cudaFuncSetAttribute(attn_split_kernel<T, NV_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    JL_LAUNCH_PDL((attn_split_kernel<T, NV_>), dim3(dim3(splits, G, B)), dim3(AS_WARPS * 32), smem, st, p, (const T*)q, (const T*)k_cache,   \
+    JL_LAUNCH_PDL((attn_split_kernel<T, NV_>), dim3(dim3(splits, G * nblk, B)), dim3(AS_WARPS * 32), smem, st, p, (const T*)q, (const T*)k_cache,   \
                                                                                (const T*)v_cache, scratch, splits);  \
   })
     const int nv = (Dv + 31) / 32;

@@ -367,16 +367,28 @@ def _nikonex_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str,
                                       H // 4, D, Dv)),
         nbytes=P * n_in * 4.0 + P * (qr + rank + R) * 2.0, like_nbytes=P * (H + 2 * H // 4) * D * 6.0)
     row = rank + R
-    qa = torch.randn(P, H * row, **bf) * 0.05
+    qd = D + R
     win_keys = sum(min(i + 1, win) for i in range(P))
-    fl = 2.0 * H * win_keys * (row + rank)
+    qf = torch.randn(P, H * qd, **bf) * 0.05
+    kf = torch.randn(P, H * qd, **bf) * 0.05
+    vf = torch.randn(P, H * Dv, **bf)
     q128 = torch.randn(P, H * D, **bf) * 0.05
     kg, vg = torch.randn(1, H // 4, T, D, **bf), torch.randn(1, H // 4, T, Dv, **bf)
     full_keys = P * (P + 1) / 2
-    add("attn_rows_kernel, windowed, shared latent rows (prompt)",
-        t.kernel(lambda: SK.attn_windowed(qa, cache, cache, zero, pad, 1, P, H, 1, row, rank, T, row, row, win, 192 ** -0.5), reps=3),
+    add("attn_rows_kernel, windowed, projected per-head keys (prompt)",
+        t.kernel(lambda: SK.attn_windowed(qf, kf, vf, zero, pad, 1, P, H, H, qd, Dv, P, H * qd, H * Dv, win, 192 ** -0.5,
+                                          strides=(P * H * qd, qd, P * H * Dv, Dv)), reps=3),
         "attn_rows_kernel (prompt)", t.kernel(lambda: SK.attn_generic(q128, kg, vg, None, zero, pad, 1, P, H, D ** -0.5), reps=3),
-        flops=fl, like_flops=2.0 * H * full_keys * (D + Dv), note="the same SIMT kernel; fractions are of the tensor-core peak")
+        flops=2.0 * H * win_keys * (qd + Dv), like_flops=2.0 * H * full_keys * (D + Dv),
+        note="the same exact SIMT kernel (heads of 192 / 128 channels fit no tensor-core attention kernel of the framework); "
+             "fractions are of the tensor-core peak")
+    cl = torch.randn(P, rank, **bf)
+    wkv = torch.randn(H * (D + Dv), rank, **bf) * 0.04
+    wqkv = torch.randn(H * (D + Dv), W, **bf) * 0.02
+    xw = torch.randn(P, W, **bf)
+    add("tcgen05 GEMM (latents up to per-head keys and values, prompt)", t.kernel(lambda: SK.linear(cl, wkv, out_f32=False)),
+        "tcgen05 GEMM (projection from the stream, same N)", t.kernel(lambda: SK.linear(xw, wqkv, out_f32=False)),
+        flops=2.0 * P * H * (D + Dv) * rank, like_flops=2.0 * P * H * (D + Dv) * W, note="the same kernel at K = latent size")
     q1 = torch.randn(1, H * row, **bf) * 0.05
     q1g = torch.randn(1, H * D, **bf) * 0.05
     add("attn_split_kernel, windowed, shared latent rows (one token)",
@@ -384,17 +396,9 @@ def _nikonex_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str,
         "attn_split_kernel (one token)", t.kernel(lambda: SK.attn_generic(q1g, kg, vg, None, ctx_len, pad, 1, 1, H, D ** -0.5)),
         nbytes=min(win, P) * row * 2.0, like_nbytes=2.0 * (H // 4) * P * D * 2.0,
         note="reads one shared latent row per key for all heads")
-    # per-head products into and out of the latent
-    qh = torch.randn(P, H * (D + R), **bf) * 0.05
+    # per-head products into and out of the latent (one token; prompts use the GEMM above)
     ukt = torch.randn(H, rank, D, **bf) * 0.05
-    qabs = torch.empty(P, H * row, **bf)
     wd = torch.randn(H * D, W, **bf) * 0.02
-    xp = torch.randn(P, W, **bf)
-    add("linear_batched (per-head map into the latent, prompt)",
-        t.kernel(lambda: SK.linear_batched(qh, ukt, qabs, nbatch=H, rows=P, x_bs=D + R, o_bs=row), reps=3),
-        "tcgen05 GEMM (q projection)", t.kernel(lambda: SK.linear(xp, wd, out_f32=False)),
-        flops=2.0 * P * H * D * rank, like_flops=2.0 * P * H * D * W,
-        note="SIMT tiles: the tensor-core GEMM takes one weight matrix per launch or per 128-row tile, not per column slice")
     q1h = torch.randn(1, H * (D + R), **bf)
     q1abs = torch.empty(1, H * row, **bf)
     x1 = torch.randn(1, W, **bf)
