@@ -429,37 +429,51 @@ __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p,
     __syncthreads();
     const int j = j0 + lane;
     const bool vis = j >= lo && j <= hi;
+    // scores of this warp's rows (lane = key): every key channel is read once for all of them; a row's sum runs in the
+    // same order as in the prompt kernel
+    float d0[AS_RW], d1[AS_RW], pj[AS_RW];
+#pragma unroll
+    for (int qi = 0; qi < AS_RW; ++qi) d0[qi] = d1[qi] = 0.0f;
+    {
+      const float4* kr = reinterpret_cast<const float4*>(Ks + lane * DP);
+      for (int c = 0; c < (DP - 4) / 4; ++c) {
+        const float4 k4 = kr[c];
+#pragma unroll
+        for (int qi = 0; qi < AS_RW; ++qi) {
+          const int r = min(warp + AS_WARPS * qi, R - 1);          // rows beyond R repeat the last one and are dropped below
+          const float4 a = reinterpret_cast<const float4*>(Qs + r * DP)[c];
+          d0[qi] = fmaf(a.x, k4.x, d0[qi]); d1[qi] = fmaf(a.y, k4.y, d1[qi]);
+          d0[qi] = fmaf(a.z, k4.z, d0[qi]); d1[qi] = fmaf(a.w, k4.w, d1[qi]);
+        }
+      }
+    }
 #pragma unroll
     for (int qi = 0; qi < AS_RW; ++qi) {
-      const int r = warp + AS_WARPS * qi;
-      if (r >= R) continue;                              // warp-uniform
-      float sc = -INFINITY;
-      if (vis) {
-        const float4* kr = reinterpret_cast<const float4*>(Ks + lane * DP);
-        const float4* qr = reinterpret_cast<const float4*>(Qs + r * DP);
-        float d0 = 0.0f, d1 = 0.0f;
-        for (int c = 0; c < (DP - 4) / 4; ++c) {
-          const float4 a = qr[c], k4 = kr[c];
-          d0 = fmaf(a.x, k4.x, d0); d1 = fmaf(a.y, k4.y, d1); d0 = fmaf(a.z, k4.z, d0); d1 = fmaf(a.w, k4.w, d1);
-        }
-        sc = (d0 + d1) * p.scale;
-      }
+      pj[qi] = 0.0f;
+      if (warp + AS_WARPS * qi >= R) continue;           // warp-uniform
+      const float sc = vis ? (d0[qi] + d1[qi]) * p.scale : -INFINITY;
       const float mnew = fmaxf(mrun[qi], warp_max(sc));
       if (mnew == -INFINITY) continue;
       const float corr = mrun[qi] == -INFINITY ? 0.0f : expf(mrun[qi] - mnew);
-      const float pj = sc == -INFINITY ? 0.0f : expf(sc - mnew);
-      lrun[qi] = lrun[qi] * corr + warp_sum(pj);
+      pj[qi] = sc == -INFINITY ? 0.0f : expf(sc - mnew);
+      lrun[qi] = lrun[qi] * corr + warp_sum(pj[qi]);
       mrun[qi] = mnew;
 #pragma unroll
       for (int i = 0; i < NV; ++i) acc[qi][i] *= corr;
-      const int jend = min(32, hi - j0 + 1);
-      for (int t = 0; t < jend; ++t) {
-        const float pt = __shfl_sync(0xffffffffu, pj, t);
-        const float* vr = Vs + t * DVP;
+    }
+    const int jend = min(32, hi - j0 + 1);
+    for (int t = 0; t < jend; ++t) {                     // every value channel is read once for all rows
+      float pt[AS_RW];
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-          const int c = lane + 32 * i;
-          if (c < p.Dv) acc[qi][i] = fmaf(pt, vr[c], acc[qi][i]);
+      for (int qi = 0; qi < AS_RW; ++qi) pt[qi] = __shfl_sync(0xffffffffu, pj[qi], t);
+      const float* vr = Vs + t * DVP;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < p.Dv) {
+          const float v = vr[c];
+#pragma unroll
+          for (int qi = 0; qi < AS_RW; ++qi) acc[qi][i] = fmaf(pt[qi], v, acc[qi][i]);
         }
       }
     }
