@@ -563,8 +563,8 @@ def test_command_line_generates_from_a_checkpoint_directory(tmp_path):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_replay_of_batches_that_come_and_go(dtype, tmp_path):
     """bin/trace_run on a saved checkpoint: a request alone, a batch of three unequal requests decoded together while
-    its shorter ones end, then a new batch after the first was given back; every wanted row against the oracle of that
-    request alone."""
+    its shorter ones end, a second batch that opens while the first is still live and goes on beside it; every wanted
+    row against the oracle of that request alone."""
     cfg = config(MIXED, vocab=80, dtype=getattr(torch, dtype))
     model = NikonexForCausalLM(cfg, seed=5, _do_init=True)
     model.save_pretrained(str(tmp_path / "m"))
@@ -577,15 +577,18 @@ def test_trace_replay_of_batches_that_come_and_go(dtype, tmp_path):
     steps.append({"step": len(steps), "entries": [{"id": "b", "tokens": seq["b"][:9], "want": [8]},
                                                    {"id": "c", "tokens": seq["c"][:41], "want": list(range(0, 41, 5))},
                                                    {"id": "d", "tokens": seq["d"][:6], "want": []}], "end": []})
-    for j in range(6):
+    for j in range(3):
         live = [("b", 9 + j, 12), ("c", 41 + j, 47), ("d", 6 + j, 9)]
-        ent = [{"id": r, "tokens": [seq[r][at]], "want": [0]} for r, at, n in live if at < n]
+        ent = [{"id": r, "tokens": [seq[r][at]], "want": [0]} for r, at, n in live]
         steps.append({"step": len(steps), "entries": ent, "end": [r for r, at, n in live if at == n - 1]})
+    # a second batch opens while the first still has a live request; from then on both go on token by token
     steps.append({"step": len(steps), "entries": [{"id": "e", "tokens": seq["e"][:20], "want": [19]},
                                                    {"id": "a2", "tokens": seq["a"][:3], "want": [2]}], "end": ["a2"]})
-    for j in range(20, 26):
-        steps.append({"step": len(steps), "entries": [{"id": "e", "tokens": [seq["e"][j]], "want": [0]}],
-                      "end": ["e"] if j == 25 else []})
+    for j in range(6):
+        ent = [{"id": "e", "tokens": [seq["e"][20 + j]], "want": [0]}]
+        if j < 3:
+            ent.insert(0, {"id": "c", "tokens": [seq["c"][44 + j]], "want": [0]})
+        steps.append({"step": len(steps), "entries": ent, "end": (["c"] if j == 2 else []) + (["e"] if j == 5 else [])})
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     out = tmp_path / "out"
     r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path / "m"), "--dtype", dtype, "--out",
