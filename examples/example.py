@@ -69,7 +69,7 @@ def load_model_dir(model_dir: str, tokenizer_path: str, is_llama3: bool, dtype: 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--ckpt_dir", help="Meta-format LLaMA checkpoint directory")
-    ap.add_argument("--model_dir", help="config.json + model.safetensors of any registered design (LLaMA, Folirax)")
+    ap.add_argument("--model_dir", help="config.json + model.safetensors of any registered design (LLaMA, Folirax, Nikonex)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="compute type with --model_dir")
     ap.add_argument("--tokenizer_path", default="")
     ap.add_argument("--is_llama3", type=lambda s: str(s).lower() in ("1", "true", "yes"), default=False)
