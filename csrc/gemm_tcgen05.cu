@@ -50,6 +50,7 @@ struct GemmParams {
   // The rows of A were ordered beforehand so that every 128-row tile belongs to one matrix (a mixture of experts).
   const int* tile_group;
   int group_rows;
+  const int* a_blocks_used;          // optional device count of leading A tiles that hold rows: the tiles after them are skipped
 };
 
 __host__ __device__ constexpr int tmem_cols_for(int bn) {
@@ -88,9 +89,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
-  const int num_tiles = p.a_blocks * p.b_blocks;
   const int ksplit = SWAP ? p.ksplit : 1;
-  const int num_work = num_tiles * ksplit;              // (tile, K split) items; split-major so neighbours differ in tile
 
   // swap-AB (decode): the next kernel of the chain may start right away — it waits for this grid itself before it
   // touches anything this grid writes — so that ITS weight prefetch (below) overlaps our epilogue
@@ -112,10 +111,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot_ptr;
   if (threadIdx.x == 0) gemm_stamp(p, 1);
 
+  int a_blocks = p.a_blocks;
   if constexpr (!SWAP) {
     pdl_wait();               // everything above overlapped the previous kernel's tail
     pdl_launch_dependents();
+    if (p.a_blocks_used != nullptr) {                     // one value for every thread of the grid: all roles walk the same list
+      const int used = *p.a_blocks_used;
+      a_blocks = used < 1 ? 1 : (used < a_blocks ? used : a_blocks);
+    }
   }
+  const int num_tiles = a_blocks * p.b_blocks;
+  const int num_work = num_tiles * ksplit;              // (tile, K split) items; split-major so neighbours differ in tile
 
   if (warp == 0) {
     // ===================================================== TMA producer
@@ -128,7 +134,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if ((int)blockIdx.x < num_work) {
           const int t = blockIdx.x % num_tiles, split = blockIdx.x / num_tiles;
           const int kb0 = split * num_kb / ksplit, kb1 = (split + 1) * num_kb / ksplit;
-          const int a_blk = t % p.a_blocks;
+          const int a_blk = t % a_blocks;
           pre = kb1 - kb0 < stages ? kb1 - kb0 : stages;
           for (int i = 0; i < pre; ++i) {
             tc::mbar_expect_tx(full_bar(i), A_BYTES + B_BYTES);
@@ -141,8 +147,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int wi = blockIdx.x; wi < num_work; wi += gridDim.x) {
         const int t = wi % num_tiles, split = wi / num_tiles;
         const int kb0 = split * num_kb / ksplit, kb1 = (split + 1) * num_kb / ksplit;
-        const int b_blk = t / p.a_blocks;
-        const int a_blk = t % p.a_blocks;
+        const int b_blk = t / a_blocks;
+        const int a_blk = t % a_blocks;
         int b_row = b_blk * BN;
         if constexpr (!SWAP) {
           if (p.tile_group != nullptr) {
@@ -198,8 +204,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if constexpr (SWAP) pdl_wait();                         // residual, output, split-K scratch: after the previous kernel
     for (int wi = blockIdx.x; wi < num_work; wi += gridDim.x, ++it) {
       const int t = wi % num_tiles, split = wi / num_tiles;
-      const int b_blk = t / p.a_blocks;
-      const int a_blk = t % p.a_blocks;
+      const int b_blk = t / a_blocks;
+      const int a_blk = t % a_blocks;
       const int as = it & 1; const uint32_t aphase = (it >> 1) & 1;
       tc::mbar_wait(tfull_bar(as), aphase);
       tc::fence_after_sync();
@@ -529,9 +535,10 @@ extern "C" JL_API int jl_gemm(const void* x, const void* w, const void* residual
 }
 
 // Grouped form of the token-major GEMM: x [M, K] with M a multiple of 128 and every 128-row tile belonging to one of
-// `groups` weight matrices w [groups][N, K]; out[m] = W_(tile_group[m / 128]) x[m] (bf16 or fp32, row pitch N).
+// `groups` weight matrices w [groups][N, K]; out[m] = W_(tile_group[m / 128]) x[m] (bf16 or fp32, row pitch N).  tiles_used
+// (optional, device): how many leading 128-row tiles hold rows; the rest are not computed.
 extern "C" JL_API int jl_gemm_grouped(const void* x, const void* w, void* out, int M, int N, int K, int groups,
-                                      const int* tile_group, int out_f32, int num_sms, void* stream) {
+                                      const int* tile_group, const int* tiles_used, int out_f32, int num_sms, void* stream) {
   JL_CHECK_ARG(M >= GEMM_BM && M % GEMM_BM == 0, "jl_gemm_grouped: M=%d must be a multiple of %d", M, GEMM_BM);
   JL_CHECK_ARG(N >= 8 && N % 8 == 0 && K >= 8 && K % 8 == 0 && groups >= 1 && tile_group != nullptr,
                "jl_gemm_grouped: bad shape N=%d K=%d groups=%d", N, K, groups);
@@ -544,6 +551,7 @@ extern "C" JL_API int jl_gemm_grouped(const void* x, const void* w, void* out, i
   p.hint_a = tc::EVICT_NORMAL; p.hint_b = tc::EVICT_LAST;
   p.tile_group = tile_group;
   p.group_rows = N;
+  p.a_blocks_used = tiles_used;
   auto s = (cudaStream_t)stream;
   if (out_f32) {
     if (N >= 256) return launch_gemm<256, EPI_PLAIN, false, true>(x, w, p, M, N, K, num_sms, s, groups);

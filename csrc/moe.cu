@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(RouteParams p)
 // One CTA orders the n = M * top pairs by expert.  counts / offsets live in shared memory (E + 1 ints each).
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, int n, int top, int E, int tile, int cap,
                                                         int* __restrict__ pos, int* __restrict__ row_src,
-                                                        int* __restrict__ tile_group) {
+                                                        int* __restrict__ tile_group, int* __restrict__ tiles_used) {
   pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
   pdl_launch_dependents();
   extern __shared__ int si[];
@@ -132,6 +132,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
     int at = 0;
     for (int e = 0; e < E; ++e) { start[e] = at; at += (count[e] + tile - 1) / tile * tile; }
     start[E] = at;
+    if (tiles_used) *tiles_used = at / tile;
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x)
@@ -203,12 +204,12 @@ extern "C" JL_API int jl_moe_route(const float* z, int ldz, int M, int E, int to
 extern "C" JL_API int jl_moe_sorted_rows(int n, int E, int tile) { return (n + E * (tile - 1) + tile - 1) / tile * tile; }
 
 extern "C" JL_API int jl_moe_sort(const int* idx, int M, int top, int E, int tile, int cap, int* pos, int* row_src, int* tile_group,
-                                  void* stream) {
+                                  int* tiles_used, void* stream) {
   JL_CHECK_ARG(M >= 1 && top >= 1 && E >= 1 && tile >= 1, "jl_moe_sort: bad shape");
   JL_CHECK_ARG(cap % tile == 0 && cap >= jl_moe_sorted_rows(M * top, E, tile), "jl_moe_sort: %d rows are too few", cap);
   const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
   JL_CHECK_ARG(smem <= 48 * 1024, "jl_moe_sort: %d experts do not fit shared memory", E);
-  JL_LAUNCH_PDL(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, idx, M * top, top, E, tile, cap, pos, row_src, tile_group);
+  JL_LAUNCH_PDL(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, idx, M * top, top, E, tile, cap, pos, row_src, tile_group, tiles_used);
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

@@ -351,18 +351,21 @@ int jl_rotary_slice(const void* in, int ldi, int in_hs, int in_off, void* out, i
 int jl_moe_route(const float* z, int ldz, int M, int E, int top, int groups, int keep, int group_top, int score, int normalise,
                  float scale, int* idx, float* wt, void* stream);
 /* Order the M * top (token, choice) pairs by expert into segments rounded up to `tile` rows (cap >= jl_moe_sorted_rows rows):
- * pos [M * top]: row of each pair; row_src [cap]: token of each row (-1: padding); tile_group [cap / tile]: expert (-1: none). */
+ * pos [M * top]: row of each pair; row_src [cap]: token of each row (-1: padding); tile_group [cap / tile]: expert (-1: none);
+ * tiles_used (optional): the number of leading tiles that belong to an expert. */
 int jl_moe_sorted_rows(int n, int E, int tile);
-int jl_moe_sort(const int* idx, int M, int top, int E, int tile, int cap, int* pos, int* row_src, int* tile_group, void* stream);
+int jl_moe_sort(const int* idx, int M, int top, int E, int tile, int cap, int* pos, int* row_src, int* tile_group,
+                int* tiles_used, void* stream);
 /* out[m] = sum_k wt[m, k] * z[pos ? pos[m*top+k] : m*top+k] (+ (gate ? sigmoid(gate[m*ldg]) : 1) * shared[m] when shared). */
 int jl_moe_combine(const float* z, int ldz, const int* pos, const float* wt, int top, const float* shared, int lds,
                    const float* gate, int ldg, float* out, int M, int W, void* stream);
 /* xs[p] = x[row_src[p]] (zeros where row_src[p] < 0): the rows of a step in sorted order; rows x W of dtype. */
 int jl_moe_gather(const void* x, int ldx, const int* row_src, void* xs, int rows, int W, int dtype, void* stream);
 /* Grouped token-major tcgen05 GEMM: x bf16 [M, K], M a multiple of 128, every 128-row tile t using the weight matrix
- * w[tile_group[t]] of w bf16 [groups][N, K] (< 0: a padding tile); out [M, N] bf16 or fp32.  N % 8 == 0, K % 8 == 0. */
+ * w[tile_group[t]] of w bf16 [groups][N, K] (< 0: a padding tile); out [M, N] bf16 or fp32.  N % 8 == 0, K % 8 == 0.
+ * tiles_used (optional, device int): only that many leading tiles are computed. */
 int jl_gemm_grouped(const void* x, const void* w, void* out, int M, int N, int K, int groups, const int* tile_group,
-                    int out_f32, int num_sms, void* stream);
+                    const int* tiles_used, int out_f32, int num_sms, void* stream);
 
 #ifdef __cplusplus
 }

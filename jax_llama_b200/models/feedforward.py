@@ -103,12 +103,12 @@ class MoeFeedForward:
             pos = None
         elif SK.tensor_cores_enabled() and h.dtype == torch.bfloat16 and W % 8 == 0 and s.ff % 8 == 0 and h.is_contiguous():
             # sorted rows in 128-row segments, gathered once, then the grouped tcgen05 GEMM twice
-            pos, row_src, tile_group = SK.moe_sort(idx, s.experts, tile=SK.GEMM_TILE_ROWS)
+            pos, row_src, tile_group, used = SK.moe_sort(idx, s.experts, tile=SK.GEMM_TILE_ROWS)
             xs = SK.moe_gather(h, row_src)
-            t = SK.gemm_grouped(xs, self.up, tile_group, act=self.act, out_f32=False)
-            y = SK.gemm_grouped(t, self.down, tile_group)
+            t = SK.gemm_grouped(xs, self.up, tile_group, act=self.act, out_f32=False, tiles_used=used)
+            y = SK.gemm_grouped(t, self.down, tile_group, tiles_used=used)
         else:
-            pos, row_src, tile_group = SK.moe_sort(idx, s.experts)
+            pos, row_src, tile_group, _ = SK.moe_sort(idx, s.experts)
             rows = row_src.shape[0]
             t = torch.empty((rows, s.ff), dtype=h.dtype, device=h.device)
             SK.linear_sorted(h, self.up, t, tile_group, row_src, act=self.act)

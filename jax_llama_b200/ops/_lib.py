@@ -78,9 +78,9 @@ _HYBRID = {
     "jl_rotary_slice": (i32, [vp, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, fp, fp, i32, ip, ip, i32, i32, i32, vp]),
     "jl_moe_route": (i32, [fp] + [i32] * 9 + [f32, ip, fp, vp]),
     "jl_moe_sorted_rows": (i32, [i32, i32, i32]),
-    "jl_moe_sort": (i32, [ip] + [i32] * 5 + [ip, ip, ip, vp]),
+    "jl_moe_sort": (i32, [ip] + [i32] * 5 + [ip, ip, ip, ip, vp]),
     "jl_moe_gather": (i32, [vp, i32, ip, vp, i32, i32, i32, vp]),
-    "jl_gemm_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, ip, i32, i32, vp]),
+    "jl_gemm_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, ip, ip, i32, i32, vp]),
     "jl_moe_combine": (i32, [fp, i32, ip, fp, i32, fp, i32, fp, i32, fp, i32, i32, vp]),
 }
 

@@ -345,9 +345,11 @@ def moe_route(z: torch.Tensor, E: int, top: int, groups: int, keep: int, group_t
     return idx, wt
 
 
-def moe_sort(idx: torch.Tensor, E: int, tile: Optional[int] = None) -> "tuple[torch.Tensor, torch.Tensor, torch.Tensor]":
-    """(pos int32 [M·top], row_src int32 [rows], tile_group int32 [rows / tile]) of the pairs ordered by expert, every
-    expert's segment rounded up to `tile` rows (default: the row tile of the SIMT grouped linear)."""
+def moe_sort(idx: torch.Tensor, E: int, tile: Optional[int] = None
+             ) -> "tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]":
+    """(pos int32 [M·top], row_src int32 [rows], tile_group int32 [rows / tile], tiles_used int32 [1]) of the pairs
+    ordered by expert, every expert's segment rounded up to `tile` rows (default: the row tile of the SIMT grouped
+    linear); tiles_used counts the leading tiles that belong to an expert."""
     L = _lib.lib()
     M, top = idx.shape
     tile = int(L.jl_linear_tile_rows()) if tile is None else int(tile)
@@ -355,9 +357,10 @@ def moe_sort(idx: torch.Tensor, E: int, tile: Optional[int] = None) -> "tuple[to
     pos = torch.empty(M * top, dtype=torch.int32, device=idx.device)
     row_src = torch.empty(cap, dtype=torch.int32, device=idx.device)
     tile_group = torch.empty(cap // tile, dtype=torch.int32, device=idx.device)
+    used = torch.empty(1, dtype=torch.int32, device=idx.device)
     _lib.check(L.jl_moe_sort(idx.data_ptr(), M, top, E, tile, cap, pos.data_ptr(), row_src.data_ptr(), tile_group.data_ptr(),
-                             _stream()), "jl_moe_sort")
-    return pos, row_src, tile_group
+                             used.data_ptr(), _stream()), "jl_moe_sort")
+    return pos, row_src, tile_group, used
 
 
 GEMM_TILE_ROWS = 128                    # row tile of the tcgen05 GEMM: the segment size of the grouped form
@@ -372,17 +375,18 @@ def moe_gather(x: torch.Tensor, row_src: torch.Tensor) -> torch.Tensor:
     return xs
 
 
-def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, *, act: int = ACT_NONE, out_f32: bool = True
-                 ) -> torch.Tensor:
+def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, *, act: int = ACT_NONE, out_f32: bool = True,
+                 tiles_used: Optional[torch.Tensor] = None) -> torch.Tensor:
     """tcgen05 GEMM over sorted rows: x bf16 [rows, K] (rows a multiple of 128, contiguous), w bf16 [n, N, K]; 128-row
-    tile t runs against w[tile_group[t]].  The activation is an in-place pass over the stored result."""
+    tile t runs against w[tile_group[t]]; with `tiles_used` (device int) only that many leading tiles are computed
+    (the rows after them are left as they are).  The activation is an in-place pass over the stored result."""
     _need(x, torch.bfloat16, "x")
     _need(w, torch.bfloat16, "w")
     n, N, K = w.shape
     rows = x.shape[0]
     out = torch.empty((rows, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     L = _lib.lib()
-    _lib.check(L.jl_gemm_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), rows, N, K, n, tile_group.data_ptr(),
+    _lib.check(L.jl_gemm_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), rows, N, K, n, tile_group.data_ptr(), _p(tiles_used),
                                  int(out_f32), num_sms(x.device), _stream()), "jl_gemm_grouped")
     if act != ACT_NONE:
         _lib.check(L.jl_act_inplace(out.data_ptr(), out.stride(0), rows, N, act, 0.0, 0.0, dtype_code(out.dtype), _stream()),

@@ -447,7 +447,7 @@ def _nikonex_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str,
     rows.append({"kernel": "moe_route (prompt)", "ms": round(t.kernel(route), 4), "like": "(none)", "like_ms": None,
                  "note": "one warp per token over the fp32 logits"})
     sort = lambda: SK.moe_sort(idx, E, tile=SK.GEMM_TILE_ROWS)                            # noqa: E731
-    pos, row_src, tile_group = sort()
+    pos, row_src, tile_group, used = sort()
     rows.append({"kernel": "moe_sort (prompt)", "ms": round(t.kernel(sort), 4), "like": "(none)", "like_ms": None,
                  "note": "one CTA orders the (token, choice) pairs by expert"})
     nrows = row_src.shape[0]
@@ -456,14 +456,14 @@ def _nikonex_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str,
     wu = torch.randn(top * ef, W, **bf) * 0.02
     fl_up = 2.0 * P * top * ef * W
     add("grouped tcgen05 GEMM + relu^2 pass (experts up)",
-        t.kernel(lambda: SK.gemm_grouped(xs, moe.up, tile_group, act=SK.ACT_RELU2, out_f32=False)),
+        t.kernel(lambda: SK.gemm_grouped(xs, moe.up, tile_group, act=SK.ACT_RELU2, out_f32=False, tiles_used=used)),
         "tcgen05 GEMM + relu^2 pass (dense up, equal active size)",
         t.kernel(lambda: SK.linear(hp, wu, act=SK.ACT_RELU2, out_f32=False)), flops=fl_up,
-        note=f"{nrows} sorted rows for {P * top} pairs (segments rounded up to 128)")
+        note=f"{int(used.item()) * 128} sorted rows for {P * top} pairs (segments rounded up to 128)")
     tmid = torch.randn(nrows, ef, **bf) * 0.1
     tdense = torch.randn(P, top * ef, **bf) * 0.1
     wdn = torch.randn(W, top * ef, **bf) * 0.02
-    add("grouped tcgen05 GEMM, fp32 out (experts down)", t.kernel(lambda: SK.gemm_grouped(tmid, moe.down, tile_group)),
+    add("grouped tcgen05 GEMM, fp32 out (experts down)", t.kernel(lambda: SK.gemm_grouped(tmid, moe.down, tile_group, tiles_used=used)),
         "tcgen05 GEMM, fp32 out (dense down, equal active size)", t.kernel(lambda: SK.linear(tdense, wdn)), flops=fl_up)
     yexp = torch.randn(nrows, W, device=dev)
     sh = torch.randn(P, W, device=dev)
