@@ -288,7 +288,7 @@ def nikonex_config(s: Dict[str, int]) -> Any:
     lat = {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": s["q_rank"], "kv_rank": s["kv_rank"],
            "scale": 192 ** -0.5, "mask": {"size": s["window"]},
            "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
-    ret = {"heads": H, "dim": 64, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(H - 1, 1)) for h in range(H)],
+    ret = {"heads": H, "dim": 64, "vdim": 128, "decay": [1.0 - 0.05 * 0.1 ** (h / max(H - 1, 1)) for h in range(H)],
            "rot": {"dims": 64, "base": 10000.0}}
     mlp = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "shared": {"ff": s["shared_ff"]},
            "router": {"experts": s["experts"], "top": s["top"], "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
