@@ -284,40 +284,61 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, 
     stage_rows<T>(Ks, DP, kbase, p.D, p.ldk, j0, hi_cta);
     stage_rows<T>(Vs, DVP, vbase, p.Dv, p.ldv, j0, hi_cta);
     __syncthreads();
+    // the warp's AR_QW queries against the tile (lane = key): every key and value channel is read once for all of them
+    int hi_q[AR_QW], lo_q[AR_QW], jend = 0;
+    bool on[AR_QW];
 #pragma unroll
     for (int qi = 0; qi < AR_QW; ++qi) {
       const int s = q0 + warp * AR_QW + qi;
-      const int hi = base + s;
-      const int lo_q = p.window > 0 ? max(lo, hi - p.window + 1) : lo;
-      if (s >= p.S || j0 > hi || j0 + 31 < lo_q) continue;      // warp-uniform
-      const int j = j0 + lane;
-      float sc = -INFINITY;
-      if (j >= lo_q && j <= hi) {
-        const float4* kr = reinterpret_cast<const float4*>(Ks + lane * DP);
-        const float4* qr = reinterpret_cast<const float4*>(Qs + (warp * AR_QW + qi) * DP);
-        float d0 = 0.0f, d1 = 0.0f;
-        for (int c = 0; c < (DP - 4) / 4; ++c) {
-          const float4 a = qr[c], k4 = kr[c];
-          d0 = fmaf(a.x, k4.x, d0); d1 = fmaf(a.y, k4.y, d1); d0 = fmaf(a.z, k4.z, d0); d1 = fmaf(a.w, k4.w, d1);
+      hi_q[qi] = base + s;
+      lo_q[qi] = p.window > 0 ? max(lo, hi_q[qi] - p.window + 1) : lo;
+      on[qi] = s < p.S && j0 <= hi_q[qi] && j0 + 31 >= lo_q[qi];         // warp-uniform
+      if (on[qi]) jend = max(jend, min(32, hi_q[qi] - j0 + 1));
+    }
+    if (jend == 0) continue;                               // no query of this warp sees the tile (the CTA's barriers are above)
+    float d0[AR_QW], d1[AR_QW], pj[AR_QW];
+#pragma unroll
+    for (int qi = 0; qi < AR_QW; ++qi) d0[qi] = d1[qi] = 0.0f;
+    {
+      const float4* kr = reinterpret_cast<const float4*>(Ks + lane * DP);
+      const float4* qr = reinterpret_cast<const float4*>(Qs + warp * AR_QW * DP);
+      for (int c = 0; c < (DP - 4) / 4; ++c) {
+        const float4 k4 = kr[c];
+#pragma unroll
+        for (int qi = 0; qi < AR_QW; ++qi) {
+          const float4 a = qr[qi * (DP / 4) + c];
+          d0[qi] = fmaf(a.x, k4.x, d0[qi]); d1[qi] = fmaf(a.y, k4.y, d1[qi]);
+          d0[qi] = fmaf(a.z, k4.z, d0[qi]); d1[qi] = fmaf(a.w, k4.w, d1[qi]);
         }
-        sc = (d0 + d1) * p.scale;
       }
+    }
+    const int j = j0 + lane;
+#pragma unroll
+    for (int qi = 0; qi < AR_QW; ++qi) {
+      pj[qi] = 0.0f;
+      if (!on[qi]) continue;
+      const float sc = (j >= lo_q[qi] && j <= hi_q[qi]) ? (d0[qi] + d1[qi]) * p.scale : -INFINITY;
       const float mnew = fmaxf(mrun[qi], warp_max(sc));
       if (mnew == -INFINITY) continue;
       const float corr = mrun[qi] == -INFINITY ? 0.0f : expf(mrun[qi] - mnew);
-      const float pj = sc == -INFINITY ? 0.0f : expf(sc - mnew);
-      lrun[qi] = lrun[qi] * corr + warp_sum(pj);
+      pj[qi] = sc == -INFINITY ? 0.0f : expf(sc - mnew);
+      lrun[qi] = lrun[qi] * corr + warp_sum(pj[qi]);
       mrun[qi] = mnew;
 #pragma unroll
       for (int i = 0; i < NV; ++i) acc[qi][i] *= corr;
-      const int jend = min(32, hi - j0 + 1);
-      for (int t = 0; t < jend; ++t) {
-        const float pt = __shfl_sync(0xffffffffu, pj, t);
-        const float* vr = Vs + t * DVP;
+    }
+    for (int t = 0; t < jend; ++t) {
+      float pt[AR_QW];
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-          const int c = lane + 32 * i;
-          if (c < p.Dv) acc[qi][i] = fmaf(pt, vr[c], acc[qi][i]);
+      for (int qi = 0; qi < AR_QW; ++qi) pt[qi] = __shfl_sync(0xffffffffu, pj[qi], t);
+      const float* vr = Vs + t * DVP;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < p.Dv) {
+          const float v = vr[c];
+#pragma unroll
+          for (int qi = 0; qi < AR_QW; ++qi) acc[qi][i] = fmaf(pt[qi], v, acc[qi][i]);
         }
       }
     }
