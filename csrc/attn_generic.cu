@@ -10,7 +10,16 @@
 //    slots [pad_left[b], slot], optional per-head output gate sigmoid(g).  Prompts of any length; exact path for
 //    float32 and for head sizes the tensor-core kernels are not built for.
 //  * attn_decode_kernel — one CTA per (row, head) for a single new token: its warps take interleaved blocks of 32 keys
-//    and merge their (max, sum, output) triples in shared memory.
+//    and merge their (max, sum, output) triples in shared memory (what runs when the caller brings no scratch).
+//  * attn_split_kernel + attn_merge_kernel — a single new token with the keys split over CTAs: a CTA stages 32-key tiles
+//    once for up to 16 query heads of a key/value head and a second launch merges the splits.
+//  * latent_prep_kernel, rotary_slice_kernel — what latent attention puts around the attention proper: norms of the
+//    query and key/value latents, rotation of the key part shared by the heads, append of one row per token; rotation
+//    of a slice of every head into another head layout.
+//
+// Keys and values are addressed by a row pitch and batch / head strides, so that the kernels read [B][G][T][d] caches,
+// one cached row per token shared by all heads (values = leading columns of the keys), or token-major projections; a
+// window limits a query to the last `window` slots up to its own.
 //
 // Input q / k / v / gate are columns of one fp32 projection buffer (row pitch ldy), as the fused projection writes them.
 #include "jllama_b200.h"

@@ -289,8 +289,8 @@ int jl_attn_prep(const float* y, int ldy, int q_off, int k_off, int v_off, void*
                  const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int dtype, void* stream);
 /* Causal softmax attention of S new tokens per row (slots *cache_len .. *cache_len+S-1) over slots [pad_left[b], own slot];
  * q [B*S, H, D], out [B*S, H, Dv]; gate (optional) fp32 [B*S, ldg], column h: out *= sigmoid(gate).
- * One new token (S == 1) with `scratch` (B*H*splits*(Dv+2) floats, splits from jl_attn_generic_splits, 0 = not available for
- * this grouping): the keys are split over `splits` CTAs per key/value head and merged by a second launch. */
+ * One new token (S == 1) with `scratch` (B*H*splits*(Dv+2) floats, splits from jl_attn_generic_splits, at most 64): the keys
+ * are split over `splits` CTAs per key/value head and block of 16 query heads, and merged by a second launch. */
 int jl_attn_generic_splits(int B, int H, int G, int T_cap);
 int jl_attn_generic(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
                     const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, float scale,
