@@ -29,6 +29,9 @@ from .feedforward import FEED_FORWARDS
 from .mixers import MIXERS, rotary_table
 
 
+BRANCH_OVERLAP_ROWS = 8        # up to this many rows the two branches of a parallel block run on two streams
+
+
 @dataclass
 class HybridCache(DeviceKVCache):
     """Per-layer caches of unequal shapes plus recurrent states.  `k` / `v` of the base class point at the first
@@ -274,22 +277,50 @@ class HybridEngine(B200Engine):
 
     def _layers_parallel(self, x: torch.Tensor, B: int, S: int, cache: HybridCache) -> torch.Tensor:
         """Parallel blocks: x += m · (mixer(norm1 x) + ff(norm2 x)).  One kernel per layer adds both branches to the
-        stream and forms the two norms the next layer reads."""
+        stream and forms the two norms the next layer reads.
+
+        With at most `BRANCH_OVERLAP_ROWS` rows (decoding) the two branches of a layer run on two streams: neither
+        fills the GPU alone and a step is a chain of short dependent kernels, so the feed-forward's chain hides behind
+        the mixer's.  Inside a graph capture the fork and join become edges of the captured graph.  Wider steps stay on
+        one stream (their tensor-core GEMMs share one split-K workspace)."""
         eps, mult = self.eps, float(self.config.residual_mult)
         n = len(self.layers)
+        overlap = B * S <= BRANCH_OVERLAP_ROWS
+        main = torch.cuda.current_stream()
         first = self.layers[0]
         h1, h2 = SK.branch_add_norm(x, None, None, mult, first.norm1, first.norm2 if first.ff is not None else None, eps)
         for i, l in enumerate(self.layers):
             rope = self._rope_for(getattr(l.mixer.spec, "rot", None), cache.capacity)
+            y2 = None
+            forked = overlap and l.ff is not None
+            if forked:
+                side, fork, join = self._branch_sync(i)
+                fork.record(main)
+                side.wait_event(fork)                      # h2 is ready
+                with torch.cuda.stream(side):
+                    y2 = l.ff.run(h2)
+                    join.record(side)
             u = l.mixer.run(h1, B, S, cache, i, rope)
             y1 = SK.linear(u, l.mixer.wo)
-            y2 = l.ff.run(h2) if l.ff is not None else None
+            if forked:
+                main.wait_event(join)
+            elif l.ff is not None:
+                y2 = l.ff.run(h2)
             nxt = self.layers[i + 1] if i + 1 < n else None
             h1, h2 = SK.branch_add_norm(x, y1, y2, mult, nxt.norm1 if nxt is not None else None,
                                         nxt.norm2 if nxt is not None and nxt.ff is not None else None, eps)
             if self.capture_streams is not None:
                 self.capture_streams.append(x.clone())
         return x
+
+    def _branch_sync(self, layer: int) -> Tuple[Any, Any, Any]:
+        """The second stream and the layer's fork / join events (made once; events without timing can be captured)."""
+        if getattr(self, "_branch_stream", None) is None:
+            self._branch_stream = torch.cuda.Stream(device=self.device)
+            self._branch_events: Dict[int, Tuple[Any, Any]] = {}
+        if layer not in self._branch_events:
+            self._branch_events[layer] = (torch.cuda.Event(), torch.cuda.Event())
+        return (self._branch_stream, *self._branch_events[layer])
 
     # ------------------------------------------------------------------ decode state
     def _decode_state(self, B: int, max_len: int) -> DecodeState:
