@@ -1,9 +1,12 @@
-"""Side-by-side throughput of a hybrid (Folirax) model and the LLaMA model of equal width, depth and head sizes, with
-random weights, plus the time of each kernel of the new design beside the like kernel of the LLaMA path.
+"""Side-by-side throughput of a newer design and the closest existing model of equal width, depth and head counts, with
+random weights, plus the time of each kernel of the new design beside the like kernel of the other path:
 
-Used by ``bench.py --compare folirax``.  Everything is timed with CUDA events on the launching stream after warm-up;
-per-kernel timings flush L2 (a 256 MB write) between iterations, whole-model timings stream more weight bytes than
-L2 holds.  Fractions are of the measured peaks in MEASURED_PEAKS.json (HBM copy bandwidth, cuBLAS bf16 burst).
+* ``bench.py --compare folirax`` — Folirax beside LLaMA (`run`),
+* ``bench.py --compare nikonex`` — Nikonex beside Folirax (`run_nikonex`).
+
+Everything is timed with CUDA events on the launching stream after warm-up; per-kernel timings flush L2 (a 256 MB write)
+between iterations, whole-model timings stream more weight bytes than L2 holds.  Fractions are of the measured peaks in
+MEASURED_PEAKS.json (HBM copy bandwidth, cuBLAS bf16 burst).
 """
 from __future__ import annotations
 
